@@ -10,11 +10,12 @@ are compile-time constants of the reference, so one pair of binaries is built pe
 Products go to baseline/_ref/ (git-ignored):  ref_all_reduce_bench_n<N>_c<C>, ref_collective_bench_n<N>_c<C>,
 libminimpi.so.
 
-    python -m baseline.build_reference [--reference <reference tree>] --ranks 2,4,8 --channels 4
+    python -m baseline.build_reference [--reference <reference tree>] --ranks 2,4,8 --channels 1,2,3,4
 """
 from __future__ import annotations
 
 import argparse
+import json
 import os
 import subprocess
 import sys
@@ -79,11 +80,23 @@ def build_variant(ref: Path, nranks: int, channels: int, jobs: int) -> list[Path
     return outs
 
 
+def default_reference_path() -> str:
+    """`reference_path` of BASELINE.json at the repository root, or the NANO_NCCL_REFERENCE variable."""
+    env = os.environ.get("NANO_NCCL_REFERENCE", "")
+    if env:
+        return env
+    try:
+        return str(json.loads((ROOT / "BASELINE.json").read_text())["reference_path"])
+    except (OSError, KeyError, ValueError):
+        return ""
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=default_reference_path(),
+                    help="the reference tree (default: reference_path of BASELINE.json)")
     ap.add_argument("--ranks", default="2,4,8")
-    ap.add_argument("--channels", default="4")
+    ap.add_argument("--channels", default="1,2,3,4")
     ap.add_argument("--jobs", type=int, default=os.cpu_count() or 4)
     args = ap.parse_args()
     ref = Path(args.reference)

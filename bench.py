@@ -10,9 +10,17 @@ with backward), reported as whole-job tokens/s.
 Rank 0 prints one JSON line.  `value` is timed on the device (CUDA events, max over ranks) with
 the inputs already resident; `e2e` times the same K steps through the public API including the
 pinned-host -> device copy of every step's tokens and the device -> host read of every step's
-loss.  `--mode collectives` instead runs the AllReduce / ReduceScatter / AllGather sweep of
-nano_nccl_b200.bench.collective_sweep.  `--impl reference` reports the reference library's arm
-(see baseline/README.md for why it is unavailable for this metric).
+loss.
+
+At 2 or more GPUs the line also carries `collectives`: the AllReduce / ReduceScatter / AllGather grid
+(float, fp16, bf16; 256 KiB .. 64 MiB x4; sum) measured in the same process right after the training
+steps, for this library and for NCCL, timed on the device (p50, max over ranks), plus `native_table`,
+this library's native benchmark programs run with the reference's host-timed loop.  `--impl reference`
+runs the unmodified reference's own benchmark programs (baseline/reference_arm.py) on the same grid at
+every channel count it is built for and reports them under the same key; the reference has no model and
+no one-rank mode, so its tokens/s value stays `unavailable`.  `--mode collectives` skips the training
+steps and makes the grid's geomean bus bandwidth the headline value.  `--impl ddp_nccl` is torch
+DistributedDataParallel over NCCL, `--impl ddp_nano` the same over this library's c10d backend "nano".
 """
 from __future__ import annotations
 
@@ -32,7 +40,12 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="nano", choices=["nano", "reference", "ddp_nccl"])
+    ap.add_argument("--impl", default="nano", choices=["nano", "reference", "ddp_nccl", "ddp_nano"])
+    ap.add_argument("--mode", default="train", choices=["train", "collectives"],
+                    help="collectives: no training steps, the headline value is the grid's geomean bus bandwidth")
+    ap.add_argument("--no-collectives", action="store_true", help="train mode: skip the collective grid after the steps")
+    ap.add_argument("--no-native-table", action="store_true", help="skip the host-timed run of the native benchmark programs")
+    ap.add_argument("--ref-budget-s", type=float, default=240.0, help="time budget of the reference's benchmark programs")
     ap.add_argument("--model", default="gpt2-medium")
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--no-overlap", action="store_true")
@@ -45,12 +58,61 @@ def parse_args():
     return ap.parse_args()
 
 
+METRIC_TRAIN = "DP training tokens/s, GPT-2-medium, BF16 (collectives: AllReduce avg of 25 MB buckets)"
+METRIC_COLLECTIVES = "AllReduce/RS/AG bus GB/s (geomean over float/fp16/bf16 x 256 KiB..64 MiB x4, sum) + p50 us per cell"
+PUBLISHED_GEOMEAN_VS_NCCL = 1.10  # the reference's published geomean of NCCL time / its own time (other hardware)
+
+
 def reference_arm(args) -> None:
-    """The reference library cannot produce this metric: it has no model, no torch binding and no
-    1-rank mode (its collective benchmark is compared separately, see baseline/compare_reference.py)."""
+    """The unmodified reference: its own benchmark programs on the collective grid (2, 4 or 8 GPUs); no
+    tokens/s value, because it has no model, no torch binding and no one-rank mode.  Under torchrun only
+    rank 0 works: the programs start their own ranks, one per GPU, under the bundled launcher."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
     from baseline.reference_arm import run_reference
 
-    print(json.dumps(run_reference(args.gpus, args.steps, args.warmup)), flush=True)
+    out = run_reference(args.gpus, args.steps, args.warmup, budget_s=args.ref_budget_s)
+    if args.mode == "collectives":
+        coll = out.get("collectives", {})
+        out.update({"metric": METRIC_COLLECTIVES, "value": coll.get("best_geomean_busbw_gbs"), "unit": "GB/s",
+                    "higher_is_better": True, "dtype": "float/fp16/bf16"})
+        if out["value"] is not None:
+            out.pop("unavailable", None)
+    print(json.dumps(out), flush=True)
+
+
+def collectives_only(args, rank, world, local, dev) -> None:
+    """--mode collectives: the grid is the whole benchmark; value = geomean bus bandwidth of this library."""
+    import torch
+    import torch.distributed as dist
+
+    from nano_nccl_b200 import _native
+    from nano_nccl_b200.bench.headline import collective_grid, native_table
+    from nano_nccl_b200.communicator import Communicator
+    from nano_nccl_b200.utils.timing import ClockSampler
+
+    if world < 2:
+        raise SystemExit("--mode collectives needs 2 or more GPUs (a collective between one rank is a copy)")
+    comm = Communicator.from_torch_distributed(device=local)
+    sampler = ClockSampler(gpu_index=local).start() if rank == 0 else None
+    grid = collective_grid(comm, world, iters=max(20, args.steps), warmup=max(5, args.warmup))
+    clocks = sampler.stop() if sampler is not None else None
+    comm.destroy()
+    dist.destroy_process_group()
+    if rank != 0:
+        return
+    ratio = grid.get("geomean_nccl_time_over_nano_time")
+    out = {"metric": METRIC_COLLECTIVES, "value": grid["geomean_busbw_gbs"], "unit": "GB/s", "n_gpus": world,
+           "steps": max(20, args.steps), "warmup": max(5, args.warmup), "ms_per_step": None, "higher_is_better": True,
+           "scaling": "weak", "vs_baseline": round(ratio / PUBLISHED_GEOMEAN_VS_NCCL, 4) if ratio else None,
+           "dtype": "float/fp16/bf16", "data": "synthetic, uniform[-1,1) seeded per rank", "impl": "nano",
+           "config": {"grid": "AR/RS/AG x float,fp16,bf16 x 256KiB..64MiB x4, sum", "l2": "flushed between iterations",
+                      "parallelism": f"{world} ranks, one per GPU"},
+           "gpu_launches": grid["nano_kernel_launches"], "clocks": clocks, "collectives": grid,
+           "native_library": _native.library_loaded_path()}
+    if not args.no_native_table:
+        out["collectives"]["native_table"] = native_table(world)
+    print(json.dumps(out), flush=True)
 
 
 def main() -> None:
@@ -74,7 +136,10 @@ def main() -> None:
     dev = torch.device("cuda", local)
     comm = None
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev)  # control plane: barriers and the max over ranks of the timings
+    if args.mode == "collectives":
+        collectives_only(args, rank, world, local, dev)
+        return
     cfg = PRESETS[args.model]
     model = build(args.model, device=dev, dtype=torch.bfloat16, seed=0)
     mb, seq = args.micro_batch, cfg.seq_len
@@ -103,8 +168,13 @@ def main() -> None:
             return loss
 
         launches_per_step = engine.launches_per_step() + nano_linears
-    else:  # torch DDP over NCCL with torch's fused AdamW: the framework-level baseline
-        ddp = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], bucket_cap_mb=25,
+    else:  # torch DDP (over NCCL, or over this library's c10d backend) with torch's fused AdamW
+        group = None
+        if world > 1 and args.impl == "ddp_nano":
+            import nano_nccl_b200.parallel.process_group  # noqa: F401  (registers the c10d backend "nano")
+
+            group = dist.new_group(backend="nano")  # gradients, buffers and the initial broadcast go through this library
+        ddp = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], bucket_cap_mb=25, process_group=group,
                                                         gradient_as_bucket_view=True) if world > 1 else model
         opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
 
@@ -172,13 +242,35 @@ def main() -> None:
 
     dev_ms = reduce_max(dev_ms)
     e2e_ms = reduce_max(e2e_ms)
+    breakdown = None
+    if args.impl == "nano" and world > 1:   # three more steps with events around every bucket's reduction (not timed above)
+        engine.enable_timeline(True)
+        for i in range(3):
+            train_step(dev_idx[i % pool], dev_tgt[i % pool])
+        breakdown = engine.timeline_summary()
+        engine.enable_timeline(False)
+    collectives = None
+    if world > 1 and args.impl == "nano" and not args.no_collectives:
+        from nano_nccl_b200.bench.headline import collective_grid
+
+        comm.set_grid_override(0)
+        collectives = collective_grid(comm, world)
+    if comm is not None:
+        comm.destroy()
+        comm = None
+    if world > 1:
+        dist.destroy_process_group()
     if rank == 0:
+        if collectives is not None and not args.no_native_table:
+            from nano_nccl_b200.bench.headline import native_table
+
+            collectives["native_table"] = native_table(world)
         value = tokens_per_step * args.steps / (dev_ms / 1e3)
         e2e_value = tokens_per_step * args.steps / (e2e_ms / 1e3)
         from nano_nccl_b200 import _native
 
         out = {
-            "metric": "DP training tokens/s, GPT-2-medium, BF16 (collectives: AllReduce avg of 25 MB buckets)",
+            "metric": METRIC_TRAIN,
             "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": round(dev_ms / args.steps, 3),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
@@ -193,11 +285,12 @@ def main() -> None:
             "clocks": clocks, "final_loss": round(final_loss, 4),
             "native_library": _native.library_loaded_path(),
         }
+        if breakdown is not None:
+            out["step_breakdown"] = breakdown
+        if collectives is not None:
+            out["collectives"] = collectives
+            out["gpu_launches_collective_grid"] = collectives["nano_kernel_launches"]
         print(json.dumps(out), flush=True)
-    if comm is not None:
-        comm.destroy()
-    if world > 1:
-        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -530,8 +530,16 @@ void Communicator::Impl::run_ring(CollectiveKind kind, const void* send, void* r
 
 void Communicator::Impl::barrier(cudaStream_t stream) {
     check_async_error();
-    if (nranks_ == 1 || !nvlink_path_) return;
+    if (nranks_ == 1) return;
     CUDA_CHECK_THROW(cudaSetDevice(device_));
+    if (!nvlink_path_) {
+        // Shared-memory, socket, RDMA or mixed edges: a one-element ring AllReduce on two internal words.  No
+        // rank's kernel completes before every rank's kernel has started, which is what a barrier promises.
+        if (barrier_words_.data() == nullptr) barrier_words_ = RawDeviceBuffer(device_, 2 * sizeof(float), true);
+        float* words = static_cast<float*>(barrier_words_.data());
+        run_ring(CollectiveKind::AllReduce, words, words + 1, 1, DType::Float, RedOp::Sum, stream);
+        return;
+    }
     order_after_previous(stream);
     CUDA_CHECK_THROW(dev::launch_barrier(dev_, 1, stream));
 }

@@ -75,6 +75,7 @@ public:
     std::unique_ptr<FdChannel> fds_;
     std::unique_ptr<SymmetricMemory> arena_;
     RawDeviceBuffer state_;
+    RawDeviceBuffer barrier_words_;  // send + receive word of barrier() on the ring transports, made on first use
     MappedU32Array status_;
     MappedU32Array abort_;
     dev::CommDev dev_{};

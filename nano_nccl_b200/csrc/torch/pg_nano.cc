@@ -83,11 +83,24 @@ nano_nccl::RedOp to_redop(const c10d::ReduceOp& op) {
 
 class WorkNano final : public c10d::Work {
 public:
-    WorkNano(int rank, c10d::OpType type, int device) : c10d::Work(rank, type), device_(device) {}
+    WorkNano(int rank, c10d::OpType type, int device, std::weak_ptr<Communicator> comm)
+        : c10d::Work(rank, type), comm_(std::move(comm)), device_(device) {}
     bool isCompleted() override { return event_.query(); }
-    bool isSuccess() const override { return true; }
+    // False once the communicator has latched an asynchronous failure (a device wait that ran out, a proxy error).
+    bool isSuccess() const override {
+        if (auto c = comm_.lock()) {
+            try {
+                c->check_async_error();
+            } catch (const std::exception&) {
+                return false;
+            }
+        }
+        return true;
+    }
+    // Stream semantics: orders the caller's current stream after the collective and returns at once, so the
+    // timeout can never run out on the host; a failure that the communicator has latched by now is thrown.
     bool wait(std::chrono::milliseconds /*timeout*/ = kNoTimeout) override {
-        // stream semantics: order the caller's current stream after the collective
+        if (auto c = comm_.lock()) c->check_async_error();
         event_.block(c10::cuda::getCurrentCUDAStream(static_cast<c10::DeviceIndex>(device_)));
         return true;
     }
@@ -101,6 +114,7 @@ public:
     c10::intrusive_ptr<c10::ivalue::Future> future_;
 
 private:
+    std::weak_ptr<Communicator> comm_;  // weak: a pending Work object must not delay the collective teardown
     int device_;
 };
 
@@ -254,7 +268,7 @@ private:
     template <typename F>
     c10::intrusive_ptr<c10d::Work> run(c10d::OpType type, std::vector<at::Tensor> tensors, F&& enqueue) {
         c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device_));
-        auto work = c10::make_intrusive<WorkNano>(getRank(), type, device_);
+        auto work = c10::make_intrusive<WorkNano>(getRank(), type, device_, comm_);
         // communication stream waits for the producer of the tensors
         at::cuda::CUDAEvent ready;
         ready.record(c10::cuda::getCurrentCUDAStream(static_cast<c10::DeviceIndex>(device_)));
@@ -275,7 +289,7 @@ private:
 
     int device_;
     c10::cuda::CUDAStream stream_;
-    std::unique_ptr<Communicator> comm_;
+    std::shared_ptr<Communicator> comm_;
     std::unique_ptr<nano_nccl::FusedGemmContext> fused_;  // after comm_: destroyed before it
     std::size_t fused_rs_bytes_ = 0, fused_ag_bytes_ = 0;
 };

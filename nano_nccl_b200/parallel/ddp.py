@@ -44,6 +44,8 @@ class _Bucket:
     ready: Optional[torch.cuda.Event] = None
     done: Optional[torch.cuda.Event] = None
     launched: bool = False
+    t_start: Optional[torch.cuda.Event] = None   # time line: the reduction starts on the communication stream
+    t_done: Optional[torch.cuda.Event] = None    # time line: the reduction has finished
 
 
 def padded_numel(numel: int) -> int:
@@ -83,6 +85,8 @@ class DataParallel:
         self.tail_full_grid = tail_full_grid
         self.shard = bool(shard_optimizer) and self.world > 1
         self.step_count = 0
+        self.timeline = False
+        self._t_forward = self._t_backward_end = self._t_step_end = None
         self.collective_launches = 0
         self.optimizer_launches = 0
         params = [p for p in module.parameters() if p.requires_grad]
@@ -139,6 +143,12 @@ class DataParallel:
     # ------------------------------------------------------------------ hooks
     def _hook(self, p: torch.Tensor) -> None:
         b = self._param_bucket[p]
+        if b.pending <= 0 or b.launched:
+            # The bucket is reduced in place: a gradient that arrives after the launch would be added on top of
+            # values that are already averaged, and no second reduction would follow.
+            raise RuntimeError("DataParallel: a gradient arrived for a bucket that was already reduced in this step "
+                               "(a second backward without zero_grad(); gradient accumulation over several backward "
+                               "passes is not supported: accumulate in the loss, or call zero_grad() between them)")
         b.pending -= 1
         if b.pending == 0 and self.overlap:
             self._launch(b)
@@ -149,6 +159,8 @@ class DataParallel:
         tail = self.tail_full_grid and self.comm_ctas > 0 and b is self.buckets[-1] and len(self.buckets) > 1
         if tail:
             self.comm.set_grid_override(0)   # the tuner's own grid for this size
+        if self.timeline:
+            b.t_start.record(self.comm_stream)
         if self.shard:
             self.comm.reduce_scatter(b.flat_grad, b.grad_shard, "avg", stream=self.comm_stream)
         else:
@@ -156,6 +168,8 @@ class DataParallel:
         if tail:
             self.comm.set_grid_override(self.comm_ctas)
         b.done.record(self.comm_stream)
+        if self.timeline:
+            b.t_done.record(self.comm_stream)
         b.launched = True
         self.collective_launches += 1
 
@@ -169,7 +183,39 @@ class DataParallel:
             b.launched = False
 
     def forward(self, *args, **kwargs):
+        if self.timeline:
+            self._t_forward.record()
         return self.module(*args, **kwargs)
+
+    # ------------------------------------------------------------------ time line
+    def enable_timeline(self, on: bool = True) -> None:
+        """Records CUDA events around every bucket's reduction and around the step, for `timeline_summary`."""
+        self.timeline = bool(on) and self.world > 1
+        if self.timeline and self._t_forward is None:
+            mk = lambda: torch.cuda.Event(enable_timing=True)
+            self._t_forward, self._t_backward_end, self._t_step_end = mk(), mk(), mk()
+            for b in self.buckets:
+                b.t_start, b.t_done = mk(), mk()
+
+    def timeline_summary(self) -> Optional[dict]:
+        """Where the last step's time went, in ms after the start of forward: when backward ended on the compute
+        stream, when the optimizer finished, and for every bucket when its reduction started and ended on the
+        communication stream.  `exposed_ms` is what the step spends after backward (waiting for the last
+        reductions plus the optimizer); `optimizer_alone_ms` is that part without any waiting, so their difference
+        is the communication that backward did not hide."""
+        if not self.timeline or self.step_count == 0:
+            return None
+        torch.cuda.synchronize()
+        t0 = self._t_forward
+        rows = [{"bytes": b.numel * 2, "start_ms": round(t0.elapsed_time(b.t_start), 3),
+                 "end_ms": round(t0.elapsed_time(b.t_done), 3)} for b in self.buckets]
+        bwd_end = t0.elapsed_time(self._t_backward_end)
+        step_end = t0.elapsed_time(self._t_step_end)
+        last_done = max(r["end_ms"] for r in rows)
+        return {"backward_end_ms": round(bwd_end, 3), "step_end_ms": round(step_end, 3),
+                "exposed_ms": round(step_end - bwd_end, 3), "last_reduction_end_ms": round(last_done, 3),
+                "reduction_after_backward_ms": round(max(0.0, last_done - bwd_end), 3),
+                "reduction_busy_ms": round(sum(r["end_ms"] - r["start_ms"] for r in rows), 3), "buckets": rows}
 
     __call__ = forward
 
@@ -177,6 +223,8 @@ class DataParallel:
         """Waits for each bucket's AllReduce, then runs the fused AdamW on it."""
         self.step_count += 1
         cur = torch.cuda.current_stream()
+        if self.timeline:
+            self._t_backward_end.record(cur)
         if self.shard and self.comm_ctas > 0:
             self.comm.set_grid_override(0)   # backward is over: the parameter gathers may use the whole GPU
         for b in self.buckets:
@@ -205,6 +253,8 @@ class DataParallel:
                 cur.wait_event(b.gathered)
             if self.comm_ctas > 0:
                 self.comm.set_grid_override(self.comm_ctas)
+        if self.timeline:
+            self._t_step_end.record(cur)
 
     def launches_per_step(self) -> int:
         """Kernels of this framework launched per training step (collectives + optimizer)."""

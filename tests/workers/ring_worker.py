@@ -55,6 +55,19 @@ def main():
     torch.cuda.synchronize()
     comm.check_async_error()
     assert comm.stats()["ring"] > 0
+    # barrier() on a ring transport really waits for the last rank: rank 1 arrives half a second late
+    import time
+
+    comm.barrier()
+    torch.cuda.synchronize()
+    if RANK == 1:
+        time.sleep(0.5)
+    t0 = time.perf_counter()
+    comm.barrier()
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - t0
+    if RANK != 1:
+        assert waited > 0.3, f"barrier returned after {waited:.3f} s although rank 1 was 0.5 s late"
     # A peer that finishes first closes its connections, which a proxy reports as a failure (a
     # closed peer cannot be told from a dead one): agree that everybody is done before leaving.
     done = torch.ones(8, device=dev)
