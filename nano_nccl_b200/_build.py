@@ -147,7 +147,64 @@ def build_core(verbose: bool = False, jobs: int | None = None) -> Path:
         objs += mobjs
     out = LIB / "libnano_nccl.so"
     _link(objs, out, link_flags, verbose, shared=True)
+    build_mpi_c_alias(out, verbose)
     return out
+
+
+def build_mpi_c_alias(core: Path, verbose: bool = False) -> Path:
+    """libnano_nccl_mpi_c.so: the name of the reference's shared C library (src/CMakeLists.txt:87-95,
+    target nano_nccl_mpi_c).  A library without code of its own that depends on libnano_nccl.so, so a
+    program that was linked against the reference's library finds the whole C ABI and the MPI C ABI when the
+    loader resolves the old name.  (`install` lays down a symbolic link instead, which also serves -l.)"""
+    alias = LIB / "libnano_nccl_mpi_c.so"
+    if alias.exists() and alias.stat().st_mtime >= core.stat().st_mtime:
+        return alias
+    _run([CXX, "-shared", "-fPIC", "-o", str(alias), "-Wl,-soname,libnano_nccl_mpi_c.so", "-Wl,--no-as-needed",
+          "-L", str(LIB), "-lnano_nccl", "-Wl,-rpath,$ORIGIN"], verbose)
+    return alias
+
+
+def install(prefix: Path, verbose: bool = False) -> dict[str, Path]:
+    """Copies the public headers, the libraries and the launcher under `prefix` (include/nano_nccl, lib, bin)
+    and writes lib/cmake/nano_nccl/nano_ncclConfig.cmake with the imported targets nano_nccl::nano_nccl and
+    nano_nccl::nano_nccl_mpi_c, the names a CMake consumer of the reference links (reference CMakeLists.txt,
+    src/CMakeLists.txt:69-95)."""
+    core = build_core(verbose)
+    build_programs(verbose)
+    prefix = Path(prefix)
+    inc, lib, bindir = prefix / "include" / "nano_nccl", prefix / "lib", prefix / "bin"
+    cmake = lib / "cmake" / "nano_nccl"
+    for d in (inc, lib, bindir, cmake):
+        d.mkdir(parents=True, exist_ok=True)
+    for h in sorted((CSRC / "include" / "nano_nccl").glob("*.h")):
+        shutil.copy2(h, inc / h.name)
+    if (CSRC / "minimpi" / "mpi.h").exists() and not have_system_mpi():
+        (prefix / "include" / "nano_nccl" / "minimpi").mkdir(exist_ok=True)
+        shutil.copy2(CSRC / "minimpi" / "mpi.h", prefix / "include" / "nano_nccl" / "minimpi" / "mpi.h")
+    shutil.copy2(core, lib / core.name)
+    # Under the installed tree the old name is a symbolic link: the link editor follows it at build time and
+    # the loader at run time.  (The in-tree alias is a dependency-only library, which serves the loader alone.)
+    alias = lib / "libnano_nccl_mpi_c.so"
+    if alias.exists() or alias.is_symlink():
+        alias.unlink()
+    alias.symlink_to(core.name)
+    for exe in ("nano_nccl_mpirun", "nano_nccl_all_reduce_bench", "nano_nccl_collective_bench"):
+        if (LIB / exe).exists():
+            shutil.copy2(LIB / exe, bindir / exe)
+    (cmake / "nano_ncclConfig.cmake").write_text(
+        "# Imported targets of the installed library: nano_nccl::nano_nccl (C++ API, C ABI, MPI C ABI) and\n"
+        "# nano_nccl::nano_nccl_mpi_c (the same entry points under the reference's library name).\n"
+        "get_filename_component(_nano_prefix \"${CMAKE_CURRENT_LIST_DIR}/../../..\" ABSOLUTE)\n"
+        "foreach(_t nano_nccl nano_nccl_mpi_c)\n"
+        "  if(NOT TARGET nano_nccl::${_t})\n"
+        "    add_library(nano_nccl::${_t} SHARED IMPORTED)\n"
+        "    set_target_properties(nano_nccl::${_t} PROPERTIES\n"
+        "      IMPORTED_LOCATION \"${_nano_prefix}/lib/lib${_t}.so\"\n"
+        "      INTERFACE_INCLUDE_DIRECTORIES \"${_nano_prefix}/include\")\n"
+        "  endif()\n"
+        "endforeach()\n"
+        "set(nano_nccl_FOUND TRUE)\n")
+    return {"include": inc, "lib": lib, "bin": bindir, "cmake": cmake}
 
 
 def build_programs(verbose: bool = False, jobs: int | None = None) -> list[Path]:
@@ -216,6 +273,11 @@ def build_all(verbose: bool = False, with_torch: bool = True) -> dict[str, objec
 
 
 if __name__ == "__main__":
+    if "--install" in sys.argv:
+        where = install(Path(sys.argv[sys.argv.index("--install") + 1]), verbose="-q" not in sys.argv)
+        for k, v in where.items():
+            print("installed", k, "->", v)
+        sys.exit(0)
     res = build_all(verbose="-q" not in sys.argv, with_torch="--no-torch" not in sys.argv)
     for k, v in res.items():
         print(k, "->", v)

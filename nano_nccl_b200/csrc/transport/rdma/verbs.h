@@ -1,5 +1,5 @@
 // The slice of the verbs API the RDMA proxies need, behind an interface, with two providers:
-// libibverbs (compiled only where <infiniband/verbs.h> exists and NANO_NCCL_ENABLE_RDMA is set)
+// libibverbs (always compiled against in-tree declarations of its ABI, bound with dlopen at run time)
 // and an in-process loopback fabric with reliable-connected semantics used by the unit tests
 // (in-order delivery, receive WQEs consumed in order, completions in order, immediate data,
 // remote-key and bounds checks on RDMA writes).
@@ -80,8 +80,8 @@ public:
 // exchange data through plain memory copies.
 std::shared_ptr<VerbsDevice> make_loopback_device(const std::string& name = "loopback0");
 
-// libibverbs provider, or nullptr (with `why`) when the library was built without RDMA support
-// or no usable device exists.
+// libibverbs provider, or nullptr (with `why`) when libibverbs.so.1 cannot be loaded or no usable
+// device exists.
 std::shared_ptr<VerbsDevice> open_ibverbs_device(const RdmaConfig& config, std::string* why);
 
 }  // namespace nano_nccl::rdma

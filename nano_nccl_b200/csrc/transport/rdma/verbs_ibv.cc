@@ -1,6 +1,7 @@
-// libibverbs provider of the verbs interface.  Compiled only when the build defines
-// NANO_NCCL_ENABLE_RDMA and <infiniband/verbs.h> exists; otherwise open_ibverbs_device() reports
-// that the library was built without it.
+// libibverbs provider of the verbs interface.  Always compiled: the verbs ABI it needs is declared in
+// ibverbs_abi.h and the library is bound at run time with dlopen, so a machine without RDMA hardware or
+// without libibverbs gets a clean "no RDMA device" answer from open_ibverbs_device() instead of a build
+// that lacks the provider.
 //
 // Parity: reference src/transport/rdma/rdma_qp.cc:93-195 (RC queue pair with one completion queue
 // shared by sends and receives, sq_sig_all = 0, max_inline_data = 64; INIT -> RTR with
@@ -8,25 +9,16 @@
 // retry 7), rdma_endpoint.cc:164-236 (device selection, port 1 ACTIVE) and rdma_gdr.cc:28-64,
 // 197-217 (GPU memory: CU_POINTER_ATTRIBUTE_SYNC_MEMOPS, then a dma-buf registration, then the
 // peer-memory registration; never a silent fall back to host memory).
-#include "transport/rdma/rdma_endpoint.h"
-#include "transport/rdma/verbs.h"
-
-#if defined(NANO_NCCL_ENABLE_RDMA) && defined(__has_include)
-#if __has_include(<infiniband/verbs.h>)
-#define NANO_NCCL_HAVE_IBVERBS 1
-#endif
-#endif
-
-#ifdef NANO_NCCL_HAVE_IBVERBS
+#include "transport/rdma/verbs_ibv.h"
 
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <dlfcn.h>
-#include <infiniband/verbs.h>
 #include <unistd.h>
 
 #include <algorithm>
 #include <cstring>
+#include <mutex>
 #include <random>
 #include <stdexcept>
 
@@ -52,10 +44,10 @@ Fn driver_entry(const char* name) {
 
 class IbvMemoryRegion final : public MemoryRegion {
 public:
-    IbvMemoryRegion(ibv_mr* mr, void* addr, std::size_t bytes, bool device, int dmabuf_fd)
-        : mr_(mr), addr_(addr), bytes_(bytes), device_(device), dmabuf_fd_(dmabuf_fd) {}
+    IbvMemoryRegion(const IbvApi& api, ibv_mr* mr, void* addr, std::size_t bytes, bool device, int dmabuf_fd)
+        : api_(api), mr_(mr), addr_(addr), bytes_(bytes), device_(device), dmabuf_fd_(dmabuf_fd) {}
     ~IbvMemoryRegion() override {
-        if (mr_ != nullptr) ibv_dereg_mr(mr_);
+        if (mr_ != nullptr) api_.dereg_mr(mr_);
         if (dmabuf_fd_ >= 0) close(dmabuf_fd_);
     }
     std::uint32_t lkey() const override { return mr_->lkey; }
@@ -66,6 +58,7 @@ public:
     bool uses_dmabuf() const override { return dmabuf_fd_ >= 0; }
 
 private:
+    const IbvApi& api_;
     ibv_mr* mr_;
     void* addr_;
     std::size_t bytes_;
@@ -74,21 +67,23 @@ private:
 };
 
 struct Shared {
+    explicit Shared(const IbvApi& a) : api(a) {}
+    const IbvApi& api;
     ibv_context* context = nullptr;
     ibv_pd* pd = nullptr;
     ibv_port_attr port{};
     ibv_gid gid{};
     HcaChoice choice;
     ~Shared() {
-        if (pd != nullptr) ibv_dealloc_pd(pd);
-        if (context != nullptr) ibv_close_device(context);
+        if (pd != nullptr) api.dealloc_pd(pd);
+        if (context != nullptr) api.close_device(context);
     }
 };
 
 class IbvQueuePair final : public QueuePair {
 public:
     IbvQueuePair(std::shared_ptr<Shared> shared, int send_depth, int recv_depth) : shared_(std::move(shared)) {
-        cq_ = ibv_create_cq(shared_->context, send_depth + recv_depth, nullptr, nullptr, 0);
+        cq_ = api().create_cq(shared_->context, send_depth + recv_depth, nullptr, nullptr, 0);
         if (cq_ == nullptr) fail("ibv_create_cq failed");
         ibv_qp_init_attr init{};
         init.send_cq = cq_;
@@ -100,9 +95,10 @@ public:
         init.cap.max_send_sge = 1;
         init.cap.max_recv_sge = 1;
         init.cap.max_inline_data = kMaxInline;
-        qp_ = ibv_create_qp(shared_->pd, &init);
+        qp_ = api().create_qp(shared_->pd, &init);
         if (qp_ == nullptr) {
-            ibv_destroy_cq(cq_);
+            api().destroy_cq(cq_);
+            cq_ = nullptr;
             fail("ibv_create_qp failed");
         }
         max_inline_ = init.cap.max_inline_data;
@@ -114,7 +110,7 @@ public:
         attr.pkey_index = 0;
         attr.port_num = static_cast<std::uint8_t>(shared_->choice.port);
         attr.qp_access_flags = kAccess;
-        if (ibv_modify_qp(qp_, &attr, IBV_QP_STATE | IBV_QP_PKEY_INDEX | IBV_QP_PORT | IBV_QP_ACCESS_FLAGS) != 0) {
+        if (api().modify_qp(qp_, &attr, IBV_QP_STATE | IBV_QP_PKEY_INDEX | IBV_QP_PORT | IBV_QP_ACCESS_FLAGS) != 0) {
             destroy();
             fail("queue pair RESET -> INIT failed");
         }
@@ -142,12 +138,12 @@ public:
         wr.sg_list = &s;
         wr.num_sge = 1;
         ibv_recv_wr* bad = nullptr;
-        if (ibv_post_recv(qp_, &wr, &bad) != 0) fail("ibv_post_recv failed");
+        if (qp_->context->ops.post_recv(qp_, &wr, &bad) != 0) fail("ibv_post_recv failed");
     }
     int poll(WorkCompletion* out, int max) override {
         constexpr int kBatch = 16;
         ibv_wc wc[kBatch];
-        const int n = ibv_poll_cq(cq_, std::min(max, kBatch), wc);
+        const int n = cq_->context->ops.poll_cq(cq_, std::min(max, kBatch), wc);
         if (n < 0) fail("ibv_poll_cq failed");
         for (int i = 0; i < n; ++i) {
             WorkCompletion& c = out[i];
@@ -155,7 +151,7 @@ public:
             c.wr_id = wc[i].wr_id;
             c.ok = wc[i].status == IBV_WC_SUCCESS;
             if (!c.ok) {
-                c.error = std::string(ibv_wc_status_str(wc[i].status)) + " (vendor error " + std::to_string(wc[i].vendor_err) + ")";
+                c.error = std::string(api().wc_status_str(wc[i].status)) + " (vendor error " + std::to_string(wc[i].vendor_err) + ")";
                 continue;  // the opcode of a failed completion is not defined
             }
             switch (wc[i].opcode) {
@@ -199,7 +195,7 @@ public:
             attr.ah_attr.grh.traffic_class = 0;
             attr.ah_attr.grh.flow_label = 0;
         }
-        if (ibv_modify_qp(qp_, &attr,
+        if (api().modify_qp(qp_, &attr,
                           IBV_QP_STATE | IBV_QP_AV | IBV_QP_PATH_MTU | IBV_QP_DEST_QPN | IBV_QP_RQ_PSN |
                               IBV_QP_MAX_DEST_RD_ATOMIC | IBV_QP_MIN_RNR_TIMER) != 0) {
             fail("queue pair INIT -> RTR failed");
@@ -211,7 +207,7 @@ public:
         rts.rnr_retry = 7;
         rts.sq_psn = psn_;
         rts.max_rd_atomic = 1;
-        if (ibv_modify_qp(qp_, &rts,
+        if (api().modify_qp(qp_, &rts,
                           IBV_QP_STATE | IBV_QP_TIMEOUT | IBV_QP_RETRY_CNT | IBV_QP_RNR_RETRY | IBV_QP_SQ_PSN |
                               IBV_QP_MAX_QP_RD_ATOMIC) != 0) {
             fail("queue pair RTR -> RTS failed");
@@ -238,14 +234,16 @@ private:
             wr.wr.rdma.rkey = rkey;
         }
         ibv_send_wr* bad = nullptr;
-        if (ibv_post_send(qp_, &wr, &bad) != 0) fail("ibv_post_send failed");
+        if (qp_->context->ops.post_send(qp_, &wr, &bad) != 0) fail("ibv_post_send failed");
     }
     void destroy() {
-        if (qp_ != nullptr) ibv_destroy_qp(qp_);
-        if (cq_ != nullptr) ibv_destroy_cq(cq_);
+        if (qp_ != nullptr) api().destroy_qp(qp_);
+        if (cq_ != nullptr) api().destroy_cq(cq_);
         qp_ = nullptr;
         cq_ = nullptr;
     }
+
+    const IbvApi& api() const { return shared_->api; }
 
     std::shared_ptr<Shared> shared_;
     ibv_cq* cq_ = nullptr;
@@ -259,9 +257,9 @@ public:
     explicit IbvDevice(std::shared_ptr<Shared> shared) : shared_(std::move(shared)) {}
     std::string name() const override { return shared_->choice.hca; }
     std::unique_ptr<MemoryRegion> register_host(void* addr, std::size_t bytes) override {
-        ibv_mr* mr = ibv_reg_mr(shared_->pd, addr, bytes, kAccess);
+        ibv_mr* mr = shared_->api.reg_mr(shared_->pd, addr, bytes, kAccess);
         if (mr == nullptr) fail("ibv_reg_mr of host memory failed");
-        return std::make_unique<IbvMemoryRegion>(mr, addr, bytes, false, -1);
+        return std::make_unique<IbvMemoryRegion>(shared_->api, mr, addr, bytes, false, -1);
     }
     std::unique_ptr<MemoryRegion> register_device(void* addr, std::size_t bytes) override {
         // Synchronous memory operations on the range, so that a copy into it is complete when the call returns.
@@ -272,25 +270,24 @@ public:
         }
         // 1. dma-buf export of the range, registered through ibv_reg_dmabuf_mr (rdma-core 34 or later).
         using GetHandle = CUresult (*)(void*, CUdeviceptr, size_t, CUmemRangeHandleType, unsigned long long);
-        using RegDmabuf = ibv_mr* (*)(ibv_pd*, std::uint64_t, std::size_t, std::uint64_t, int, int);
         auto get_handle = driver_entry<GetHandle>("cuMemGetHandleForAddressRange");
-        auto reg_dmabuf = reinterpret_cast<RegDmabuf>(dlsym(RTLD_DEFAULT, "ibv_reg_dmabuf_mr"));
+        auto reg_dmabuf = shared_->api.reg_dmabuf_mr;
         if (get_handle != nullptr && reg_dmabuf != nullptr) {
             int fd = -1;
             if (get_handle(&fd, reinterpret_cast<CUdeviceptr>(addr), bytes, CU_MEM_RANGE_HANDLE_TYPE_DMA_BUF_FD, 0) ==
                     CUDA_SUCCESS && fd >= 0) {
                 ibv_mr* mr = reg_dmabuf(shared_->pd, 0, bytes, reinterpret_cast<std::uint64_t>(addr), fd, kAccess);
-                if (mr != nullptr) return std::make_unique<IbvMemoryRegion>(mr, addr, bytes, true, fd);
+                if (mr != nullptr) return std::make_unique<IbvMemoryRegion>(shared_->api, mr, addr, bytes, true, fd);
                 close(fd);
             }
         }
         // 2. the peer-memory path: the HCA driver resolves the GPU address itself.
-        ibv_mr* mr = ibv_reg_mr(shared_->pd, addr, bytes, kAccess);
+        ibv_mr* mr = shared_->api.reg_mr(shared_->pd, addr, bytes, kAccess);
         if (mr == nullptr) {
             fail("GPU memory could not be registered (neither dma-buf nor peer memory); GPUDirect was requested "
                  "explicitly, so host staging is not used instead");
         }
-        return std::make_unique<IbvMemoryRegion>(mr, addr, bytes, true, -1);
+        return std::make_unique<IbvMemoryRegion>(shared_->api, mr, addr, bytes, true, -1);
     }
     std::unique_ptr<QueuePair> create_qp(int send_depth, int recv_depth) override {
         return std::make_unique<IbvQueuePair>(shared_, send_depth, recv_depth);
@@ -303,27 +300,75 @@ private:
 
 }  // namespace
 
+const IbvApi* load_ibverbs(std::string* why) {
+    static std::once_flag once;
+    static IbvApi api;
+    static std::string problem;
+    static bool ok = false;
+    std::call_once(once, [] {
+        void* lib = dlopen("libibverbs.so.1", RTLD_NOW | RTLD_GLOBAL);
+        if (lib == nullptr) {
+            problem = "no RDMA device: libibverbs.so.1 cannot be loaded on this machine";
+            return;
+        }
+        auto bind = [&](auto& slot, const char* name, bool required) {
+            slot = reinterpret_cast<std::remove_reference_t<decltype(slot)>>(dlsym(lib, name));
+            if (slot == nullptr && required && problem.empty()) problem = std::string("libibverbs.so.1 lacks ") + name;
+        };
+        bind(api.get_device_list, "ibv_get_device_list", true);
+        bind(api.free_device_list, "ibv_free_device_list", true);
+        bind(api.get_device_name, "ibv_get_device_name", true);
+        bind(api.open_device, "ibv_open_device", true);
+        bind(api.close_device, "ibv_close_device", true);
+        bind(api.query_port, "ibv_query_port", true);
+        bind(api.query_gid, "ibv_query_gid", true);
+        bind(api.alloc_pd, "ibv_alloc_pd", true);
+        bind(api.dealloc_pd, "ibv_dealloc_pd", true);
+        bind(api.reg_mr, "ibv_reg_mr", true);
+        bind(api.reg_dmabuf_mr, "ibv_reg_dmabuf_mr", false);  // rdma-core 34 or later
+        bind(api.dereg_mr, "ibv_dereg_mr", true);
+        bind(api.create_cq, "ibv_create_cq", true);
+        bind(api.destroy_cq, "ibv_destroy_cq", true);
+        bind(api.create_qp, "ibv_create_qp", true);
+        bind(api.modify_qp, "ibv_modify_qp", true);
+        bind(api.destroy_qp, "ibv_destroy_qp", true);
+        bind(api.wc_status_str, "ibv_wc_status_str", true);
+        ok = problem.empty();
+    });
+    if (!ok) {
+        if (why != nullptr) *why = problem;
+        return nullptr;
+    }
+    return &api;
+}
+
+std::shared_ptr<VerbsDevice> open_ibverbs_device_with(const IbvApi& api, const HcaChoice& choice) {
+    int count = 0;
+    ibv_device** list = api.get_device_list(&count);
+    if (list == nullptr || count == 0) fail("no RDMA device: ibv_get_device_list found none");
+    auto shared = std::make_shared<Shared>(api);
+    shared->choice = choice;
+    for (int i = 0; i < count && shared->context == nullptr; ++i) {
+        if (choice.hca == api.get_device_name(list[i])) shared->context = api.open_device(list[i]);
+    }
+    api.free_device_list(list);
+    if (shared->context == nullptr) fail("ibv_open_device(" + choice.hca + ") failed");
+    if (api.query_port(shared->context, static_cast<std::uint8_t>(choice.port), &shared->port) != 0) fail("ibv_query_port failed");
+    if (shared->port.state != IBV_PORT_ACTIVE) fail("port " + std::to_string(choice.port) + " of " + choice.hca + " is not ACTIVE");
+    if (api.query_gid(shared->context, static_cast<std::uint8_t>(choice.port), choice.gid_index, &shared->gid) != 0) {
+        fail("ibv_query_gid(" + std::to_string(choice.gid_index) + ") failed");
+    }
+    shared->pd = api.alloc_pd(shared->context);
+    if (shared->pd == nullptr) fail("ibv_alloc_pd failed");
+    return std::make_shared<IbvDevice>(std::move(shared));
+}
+
 std::shared_ptr<VerbsDevice> open_ibverbs_device(const RdmaConfig& config, std::string* why) {
     try {
+        const IbvApi* api = load_ibverbs(why);
+        if (api == nullptr) return nullptr;
         const HcaChoice choice = select_hca(config.ifname, config.gid_index, interface_gids(config.ifname));
-        int count = 0;
-        ibv_device** list = ibv_get_device_list(&count);
-        if (list == nullptr || count == 0) fail("ibv_get_device_list found no device");
-        auto shared = std::make_shared<Shared>();
-        shared->choice = choice;
-        for (int i = 0; i < count; ++i) {
-            if (choice.hca == ibv_get_device_name(list[i])) shared->context = ibv_open_device(list[i]);
-        }
-        ibv_free_device_list(list);
-        if (shared->context == nullptr) fail("ibv_open_device(" + choice.hca + ") failed");
-        if (ibv_query_port(shared->context, static_cast<std::uint8_t>(choice.port), &shared->port) != 0) fail("ibv_query_port failed");
-        if (shared->port.state != IBV_PORT_ACTIVE) fail("port 1 of " + choice.hca + " is not ACTIVE");
-        if (ibv_query_gid(shared->context, static_cast<std::uint8_t>(choice.port), choice.gid_index, &shared->gid) != 0) {
-            fail("ibv_query_gid(" + std::to_string(choice.gid_index) + ") failed");
-        }
-        shared->pd = ibv_alloc_pd(shared->context);
-        if (shared->pd == nullptr) fail("ibv_alloc_pd failed");
-        return std::make_shared<IbvDevice>(std::move(shared));
+        return open_ibverbs_device_with(*api, choice);
     } catch (const std::exception& e) {
         if (why != nullptr) *why = e.what();
         return nullptr;
@@ -331,18 +376,3 @@ std::shared_ptr<VerbsDevice> open_ibverbs_device(const RdmaConfig& config, std::
 }
 
 }  // namespace nano_nccl::rdma
-
-#else  // no libibverbs at build time
-
-namespace nano_nccl::rdma {
-
-std::shared_ptr<VerbsDevice> open_ibverbs_device(const RdmaConfig&, std::string* why) {
-    if (why != nullptr) {
-        *why = "this build has no libibverbs provider (NANO_NCCL_ENABLE_RDMA was not set or <infiniband/verbs.h> is missing)";
-    }
-    return nullptr;
-}
-
-}  // namespace nano_nccl::rdma
-
-#endif

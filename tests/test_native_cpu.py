@@ -8,7 +8,7 @@ import pytest
 TESTS = Path(__file__).resolve().parent.parent / "nano_nccl_b200" / "lib" / "tests"
 CPU_PROGRAMS = ["bootstrap_test", "c_api", "simple_protocol_test", "socket_protocol_test", "host_ring_test",
                 "rdma_protocol_test", "rdma_proxy_test", "rdma_timeline_test", "rdma_endpoint_test", "topology_tuner_test",
-                "ring_turnaround_test"]
+                "ring_turnaround_test", "rdma_ibv_contract_test"]
 
 
 @pytest.mark.parametrize("name", CPU_PROGRAMS)
@@ -70,3 +70,27 @@ def test_launcher_time_limit_ends_hanging_ranks(native_build):
                        capture_output=True, text=True, timeout=60)
     assert p.returncode != 0
     assert time.time() - t0 < 20, "the launcher did not enforce its limit"
+
+
+def test_install_tree_serves_a_c_program_under_the_reference_library_name(native_build, tmp_path):
+    """`_build.install(prefix)` lays out include/, lib/ and a CMake package; a plain C program compiled against the
+    installed headers and linked only with -lnano_nccl_mpi_c (the reference's shared library name) runs."""
+    import subprocess
+
+    where = native_build.install(tmp_path / "prefix")
+    assert (where["include"] / "nano_nccl.h").exists() and (where["include"] / "mpi_c_api.h").exists()
+    assert (where["lib"] / "libnano_nccl.so").exists() and (where["lib"] / "libnano_nccl_mpi_c.so").exists()
+    assert "nano_nccl::nano_nccl_mpi_c" in (where["cmake"] / "nano_ncclConfig.cmake").read_text()
+    src = tmp_path / "abi.c"
+    src.write_text('#include <nano_nccl/nano_nccl.h>\n#include <stdio.h>\n'
+                   'int main(void) {\n'
+                   '    if (nano_nccl_abi_version() != NANO_NCCL_ABI_VERSION) return 1;\n'
+                   '    if (nano_nccl_destroy_communicator(NULL) != NANO_NCCL_STATUS_SUCCESS) return 2;\n'
+                   '    printf("abi %u via the alias\\n", nano_nccl_abi_version());\n    return 0;\n}\n')
+    exe = tmp_path / "abi"
+    cuda_inc = str(native_build.CUDA_HOME / "include")
+    subprocess.run(["gcc", "-std=c11", "-I", str(tmp_path / "prefix" / "include"), "-I", cuda_inc, str(src), "-o", str(exe),
+                    "-L", str(where["lib"]), "-lnano_nccl_mpi_c", "-Wl,-rpath," + str(where["lib"]),
+                    "-Wl,-rpath-link," + str(where["lib"])], check=True, capture_output=True, text=True)
+    p = subprocess.run([str(exe)], capture_output=True, text=True, timeout=60)
+    assert p.returncode == 0 and "abi 2 via the alias" in p.stdout, p.stdout + p.stderr

@@ -36,14 +36,6 @@ def test_everything_is_built_for_sm_100a_only():
             assert forbidden not in _text(p), f"{p} mentions {forbidden}"
 
 
-def test_batched_memcpy_calls_are_never_named():
-    names = ["cudaMemcpy" + "BatchAsync", "cudaMemcpy3D" + "BatchAsync", "cuMemcpy" + "BatchAsync", "cuMemcpy3D" + "BatchAsync"]
-    for p in NATIVE + PYTHON:
-        text = _text(p)
-        for n in names:
-            assert n not in text, f"{p} names {n}"
-
-
 def test_device_code_cannot_trap_or_spin_forever():
     for p in DEVICE:
         text = _text(p)
