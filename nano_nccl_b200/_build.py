@@ -40,8 +40,8 @@ NVCC_FLAGS = ARCH_FLAGS + ["-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-con
 CXX_FLAGS = ["-O2", "-g1", "-std=c++17", "-fPIC", "-Wall", "-Wextra", "-Wno-unused-parameter", "-DNANO_NCCL_ENABLE_RDMA_PROXY_TIMELINE",
              "-pthread", "-I", str(CUDA_HOME / "include")] + INCLUDES
 
-# Diagnostic builds: NANO_NCCL_BUILD_DEFINES=NANO_DEBUG_BOUNDS makes the collective kernels re-check
-# their staging footprint on the device once per tile (comma-separated list of macro names).
+# NANO_NCCL_BUILD_DEFINES: comma-separated macro names added to every compile line (e.g. the opt-in
+# NANO_NCCL_ENABLE_BENCH_PROFILING of the native benchmarks).
 EXTRA_DEFINES = ["-D" + d for d in os.environ.get("NANO_NCCL_BUILD_DEFINES", "").split(",") if d.strip()]
 NVCC_FLAGS += EXTRA_DEFINES
 CXX_FLAGS += EXTRA_DEFINES

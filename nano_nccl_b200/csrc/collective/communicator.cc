@@ -10,6 +10,7 @@
 // latched asynchronous error every call throws the same stable message; device selection is
 // agreed collectively so that no rank is left waiting in a control collective.
 #include "collective/communicator_impl.h"
+#include "collective/teardown.h"
 #include "collective/signature.h"
 
 #include "core/env.h"
@@ -210,9 +211,35 @@ Communicator::Impl::~Impl() {
     if (status_.size() != 0 && status_.host()[0] != 0 && abort_.size() != 0) {
         abort_.host()[0] = 1;
     }
-    cudaSetDevice(device_);
-    cudaDeviceSynchronize();
+    cudaError_t drained = cudaSetDevice(device_);
+    if (drained == cudaSuccess) drained = cudaDeviceSynchronize();
     cudaGetLastError();
+    if (env::flag("NANO_NCCL_TEST_TEARDOWN_FAILURE", false)) drained = cudaErrorUnknown;  // host-side injection for tests
+    TeardownAction action = TeardownAction::Quarantine;
+    try {
+        action = decide_teardown(drained != cudaSuccess, env::get("NANO_NCCL_TEARDOWN").value_or(""));
+    } catch (const std::exception& e) {
+        std::fprintf(stderr, "nano_nccl: %s; using 'quarantine'\n", e.what());
+        action = drained != cudaSuccess ? TeardownAction::Quarantine : TeardownAction::Release;
+    }
+    if (action != TeardownAction::Release) {
+        std::fprintf(stderr,
+                     "nano_nccl: rank %d could not drain its GPU work while destroying a communicator (%s); %s\n", rank_,
+                     cudaGetErrorString(drained),
+                     action == TeardownAction::Abort
+                         ? "NANO_NCCL_TEARDOWN=abort: ending the process"
+                         : "leaving its device memory mapped (a kernel or a peer may still use it)");
+        if (action == TeardownAction::Abort) std::terminate();
+        // Quarantine: the owners are released without running their destructors.
+        (void)ring_.release();
+        for (auto& segment : heap_) (void)segment.release();
+        (void)ll_arena_.release();
+        (void)arena_.release();
+        (void)fds_.release();
+        state_.leak();
+        barrier_words_.leak();
+        return;
+    }
     ring_.reset();
     heap_.clear();
     ll_arena_.reset();

@@ -31,6 +31,8 @@ public:
     std::size_t bytes() const noexcept { return bytes_; }
     int device() const noexcept { return device_; }
     void release() noexcept;
+    // Forgets the allocation without freeing it (teardown after a failed drain: a kernel may still use it).
+    void leak() noexcept { ptr_ = nullptr; bytes_ = 0; }
 
 private:
     void swap(RawDeviceBuffer& o) noexcept {

@@ -20,22 +20,29 @@
  *   - nranks from 1 to NANO_NCCL_NOALLOC_MAX_RANKS (8);
  *   - count from 1 to NANO_NCCL_NOALLOC_MAX_COUNT (4 Mi elements) per buffer;
  *   - the scratch array takes NANO_NCCL_NOALLOC_SCRATCH_BYTES (about 16.6 MiB) of device memory on
- *     every GPU that loads this library, from load until the process exits, used or not.
+ *     every GPU on which this library's device code gets loaded, until the process exits, used or
+ *     not.  The CUDA runtime loads device code lazily by default: the array (and the code of each
+ *     kernel variant) is then placed on a device by the first call that needs it there, and that
+ *     placement is an allocation made by the driver on this library's behalf.
  * Requests beyond the limits are refused with NANO_NCCL_STATUS_INVALID_ARGUMENT and a message in
  * nano_nccl_get_last_error(); nothing is launched.
  *
  * Rules for callers:
  *   - The first call on each device looks up the device address of the scratch array
- *     (cudaGetSymbolAddress, with that device current).  Make that first call before any stream
- *     capture begins on the calling thread.
+ *     (cudaGetSymbolAddress, with that device current), and the first call of each (dtype,
+ *     operator) pair makes the driver load that kernel.  Make those first calls at start-up, once
+ *     per device and per variant you will use, before the no-allocation regime begins and before
+ *     any stream capture begins on the calling thread; later calls allocate nothing anywhere.
  *   - Every call uses the same scratch array, and the array keeps whatever the previous call left
  *     in it; the control part (signal pads, counters, status) is cleared on `stream` at the start
  *     of every call.  Two calls whose kernels may overlap on the GPU (different streams, or the
  *     same buffers used from two threads) race on the scratch and give wrong results: order them.
  *   - Buffers must not overlap each other; srcs[r] == dsts[r] is not allowed.
  *   - A wait that runs out inside the kernel (it cannot happen unless the launch was starved of
- *     SMs for seconds) ends the kernel early and leaves the outputs incomplete; this entry point
- *     has nowhere to report that asynchronously, so check results on first use in a new setting.
+ *     SMs for seconds) ends the kernel early and leaves the outputs incomplete.  The kernel notes
+ *     that in status words inside the scratch array; nano_nccl_all_reduce_local_noalloc_status()
+ *     waits for `stream` and reads them back (into caller memory, without allocating).  Call it
+ *     before the next AllReduce on the device, which clears the words.
  * It calls no cudaMalloc, cudaFree, cudaHostAlloc or any allocating routine of another library. */
 #ifndef NANO_NCCL_NANO_NCCL_NOALLOC_H_
 #define NANO_NCCL_NANO_NCCL_NOALLOC_H_
@@ -55,6 +62,12 @@ nano_nccl_status_t nano_nccl_all_reduce_local_noalloc(const void* const* srcs, v
                                                       int nranks, size_t count,
                                                       nano_nccl_dtype_t dtype,
                                                       nano_nccl_redop_t redop, cudaStream_t stream);
+
+/* Synchronous: waits for `stream`, then copies the status words of the last call on the current device into
+ * words[0..3] = {code, peer rank, phase, block}; all zero and NANO_NCCL_STATUS_SUCCESS when every wait of that
+ * call was satisfied, the first failing rank's words and NANO_NCCL_STATUS_ERROR otherwise.  Allocates nothing.
+ * No counterpart in the reference. */
+nano_nccl_status_t nano_nccl_all_reduce_local_noalloc_status(cudaStream_t stream, uint32_t words[4]);
 
 #ifdef __cplusplus
 }

@@ -74,22 +74,18 @@ __device__ __forceinline__ void save_state(const CommDev& c, std::uint32_t epoch
     }
 }
 
-// Builds with -DNANO_DEBUG_BOUNDS re-check on the device, once per tile, that the staging footprint
-// the host computed fits this block's staging half: `slots` slots of `slot_bytes` inside
-// `area_bytes`, of which a slot uses `used_bytes`.  A violation is recorded as kStatusBadArgument
-// {slots, used_bytes / 16} and the block leaves before touching staging (its peers' waits then run
-// out and report the same call).  The answer is uniform over the block.  Other builds: always true.
+// Every kernel re-checks on the device, once per tile, that the staging footprint the host computed fits
+// this block's staging half: `slots` slots of `slot_bytes` inside `area_bytes`, of which a slot uses
+// `used_bytes`.  A violation is recorded as kStatusBadArgument {slots, used_bytes / 16} and the block leaves
+// before touching staging (its peers' waits then run out and report the same call).  The answer is uniform
+// over the block; the check is a handful of integer operations per tile, so it is part of every build (the
+// stand-in for a memory checker, which the target machines do not offer).
 __device__ __forceinline__ bool tile_fits(const CommDev& c, std::size_t used_bytes, std::size_t slot_bytes, int slots,
                                           std::size_t area_bytes) {
-#ifdef NANO_DEBUG_BOUNDS
     const bool ok = blockIdx.x < static_cast<unsigned>(kMaxBlocks) && slot_bytes % 16 == 0 && used_bytes <= slot_bytes &&
                     static_cast<std::size_t>(slots) * slot_bytes <= area_bytes;
     if (!ok && threadIdx.x == 0) report_status(c, kStatusBadArgument, slots, static_cast<int>(used_bytes >> 4));
     return ok;
-#else
-    (void)c; (void)used_bytes; (void)slot_bytes; (void)slots; (void)area_bytes;
-    return true;
-#endif
 }
 
 // Largest sub-slice of a tile of n elements split over N owners, in bytes of whole 16-byte vectors.

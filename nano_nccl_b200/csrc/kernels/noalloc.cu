@@ -131,3 +131,34 @@ extern "C" nano_nccl_status_t nano_nccl_all_reduce_local_noalloc(const void* con
     }
     return NANO_NCCL_STATUS_SUCCESS;
 }
+
+extern "C" nano_nccl_status_t nano_nccl_all_reduce_local_noalloc_status(cudaStream_t stream, uint32_t words[4]) {
+    using namespace nano_nccl::c_api;
+    begin_call();
+    if (words == nullptr) return fail(NANO_NCCL_STATUS_INVALID_ARGUMENT, "words must be non-null");
+    words[0] = words[1] = words[2] = words[3] = 0;
+    unsigned char* scratch = nullptr;
+    if (scratch_for_current_device(&scratch) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(NANO_NCCL_STATUS_ERROR, "cudaGetSymbolAddress of the scratch array failed on the current device");
+    }
+    if (cudaStreamSynchronize(stream) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(NANO_NCCL_STATUS_ERROR, "waiting for the stream failed");
+    }
+    // eight status words per rank, on the stack: no allocation here either
+    std::uint32_t all[8 * kRanksMax] = {};
+    const unsigned char* status = scratch + kRanksMax * sizeof(BlockState) * kMaxBlocks;
+    if (cudaMemcpy(all, status, sizeof(all), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(NANO_NCCL_STATUS_ERROR, "reading the status words failed");
+    }
+    for (int r = 0; r < kRanksMax; ++r) {
+        if (all[8 * r] != 0) {
+            for (int k = 0; k < 4; ++k) words[k] = all[8 * r + k];
+            return fail(NANO_NCCL_STATUS_ERROR,
+                        "the last allocation-free AllReduce on this device ended early: a bounded wait ran out; its outputs are incomplete");
+        }
+    }
+    return NANO_NCCL_STATUS_SUCCESS;
+}

@@ -6,6 +6,7 @@
 #include "kernels/launch.h"
 #include "test_util.h"
 #include "gemm/gemm.h"
+#include "collective/teardown.h"
 #include "topology/topology.h"
 
 #include <algorithm>
@@ -25,6 +26,16 @@ static std::vector<RankInfo> ranks(int n, int per_host, bool peer_access) {
 }
 
 int main() {
+    {   // teardown policy: release when the drain worked; otherwise quarantine unless fail-stop was asked for
+        using nano_nccl::TeardownAction;
+        using nano_nccl::decide_teardown;
+        CHECK(decide_teardown(false, "") == TeardownAction::Release);
+        CHECK(decide_teardown(false, "abort") == TeardownAction::Release);
+        CHECK(decide_teardown(true, "") == TeardownAction::Quarantine);
+        CHECK(decide_teardown(true, "quarantine") == TeardownAction::Quarantine);
+        CHECK(decide_teardown(true, "abort") == TeardownAction::Abort);
+        CHECK_THROWS_WITH(decide_teardown(true, "ignore"), "NANO_NCCL_TEARDOWN");
+    }
     {   // topology validation
         ProcessTopology t;
         t.global_rank_count = 4;

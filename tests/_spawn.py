@@ -10,10 +10,29 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def free_port() -> int:
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        return s.getsockname()[1]
+def free_port(span: int = 8) -> int:
+    """A port p such that p .. p + span - 1 can all be bound right now.  Taken below the range the kernel hands
+    out for outgoing connections (32768 and up), so that a rank's own client socket can never sit on a port
+    that a worker wants to listen on next (workers use NANO_TEST_PORT + small offsets)."""
+    import random
+
+    rng = random.Random(os.getpid() * 7919 + int.from_bytes(os.urandom(4), "little"))
+    for _ in range(200):
+        base = rng.randrange(15000, 31000, span)
+        socks = []
+        try:
+            for k in range(span):
+                s = socket.socket()
+                socks.append(s)
+                s.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+                s.bind(("127.0.0.1", base + k))
+            return base
+        except OSError:
+            continue
+        finally:
+            for s in socks:
+                s.close()
+    raise RuntimeError("no free port range found")
 
 
 def run_ranks(worker: str, nranks: int, args: list[str] | None = None, env: dict | None = None,

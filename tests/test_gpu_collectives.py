@@ -14,7 +14,8 @@ def _ranks():
     return 8 if n >= 8 else 4 if n >= 4 else 2
 
 
-@pytest.mark.parametrize("mode", ["matrix", "nan", "invalid", "symmetric", "large"])
+@pytest.mark.parametrize("mode", ["matrix", "nan", "invalid", "symmetric", "large", "symmetric_rs_ag", "symmetric_pool",
+                                  "registered", "graph"])
 def test_collective_matrix(mode):
     outs = run_ranks("collective_worker.py", _ranks(), [mode], timeout=600)
     assert all(f"{mode} ok" in o for o in outs), outs

@@ -81,3 +81,131 @@ def test_nothing_committed_depends_on_scratch():
         if p.name == "test_source_contracts.py":
             continue
         assert "_work/" not in _text(p) and "_work." not in _text(p), p
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Ordering and ownership contracts that mirror the reference's source-text tests one by one
+# (reference tests/*_static.py); each names the file of the reference it corresponds to.
+
+def _body(text: str, signature: str) -> str:
+    """Text of the function whose definition starts with `signature` (brace matched)."""
+    start = text.find(signature)
+    assert start >= 0, f"missing function: {signature}"
+    depth, i = 0, text.find("{", start)
+    for j in range(i, len(text)):
+        depth += text[j] == "{"
+        depth -= text[j] == "}"
+        if depth == 0:
+            return text[start:j + 1]
+    raise AssertionError(f"unterminated function: {signature}")
+
+
+def _in_order(text: str, fragments: list) -> None:
+    pos = 0
+    for f in fragments:
+        nxt = text.find(f, pos)
+        assert nxt >= 0, f"missing or out of order: {f}"
+        pos = nxt + len(f)
+
+
+def test_every_collective_checks_the_latched_error_then_validates():
+    """collective_scope_static.py: all three entry points, in this order, and none rejects distributed communicators."""
+    src = _text(PKG / "csrc" / "collective" / "communicator.cc")
+    for name, args in (("all_reduce", "AllReduceArgs"), ("reduce_scatter", "ReduceScatterArgs"), ("all_gather", "AllGatherArgs")):
+        body = _body(src, f"void Communicator::Impl::{name}(const {args}& a)")
+        _in_order(body, ["check_async_error();", "validate_args("])
+        assert "distributed" not in body
+    assert "a.redop" not in _body(src, "void Communicator::Impl::all_gather(const AllGatherArgs& a)")  # AllGather has no operator
+
+
+def test_avg_scale_is_fused_into_the_final_reduce():
+    """avg_scale_fusion_static.py: the 1/N factor is applied where the last partial is combined, never by a pass of its own."""
+    device = "".join(_text(p) for p in DEVICE)
+    assert not re.search(r"__global__[^;{]*\bscale\w*\s*\(", device), "a stand-alone scaling kernel exists"
+    coll = _text(PKG / "csrc" / "kernels" / "collectives.cuh")
+    prims = _text(PKG / "csrc" / "kernels" / "prims.cuh")
+    assert "finish<Op, T>(acc, inv)" in coll, "the collective kernels no longer scale in finish()"
+    assert "RedOpTraits<Op>::kScales" in _body(prims, "__device__ __forceinline__ void finish("), "finish() does not key the scale on the operator"
+    ring = _text(PKG / "csrc" / "kernels" / "ring_simple.cuh")
+    assert "if (kFinal) finish<Op, T>(acc, inv);" in ring and ring.count("finish<Op, T>") == 1, "the ring scales outside its final combine"
+
+
+def test_teardown_has_a_decided_policy_for_a_failed_drain():
+    """communicator_cleanup_static.py: a CUDA failure while draining is never ignored; the destructor either ends the
+    process (the reference's behaviour, on request) or leaves every mapping in place, and says so."""
+    src = _text(PKG / "csrc" / "collective" / "communicator.cc")
+    body = _body(src, "Communicator::Impl::~Impl()")
+    _in_order(body, ["cudaDeviceSynchronize()", "decide_teardown(", "std::terminate()", "arena_.release()", "arena_.reset()"])
+    policy = _text(PKG / "csrc" / "collective" / "teardown.h")
+    assert "Quarantine" in policy and "Abort" in policy
+
+
+def test_benchmark_profiling_hooks_are_off_by_default():
+    """bench_profiling_static.py: NVTX / profiler calls exist only under the opt-in macro, which no default build sets."""
+    hooks = _text(PKG / "csrc" / "bench" / "bench_profiling.h")
+    assert hooks.count("#if defined(NANO_NCCL_ENABLE_BENCH_PROFILING)") >= 3
+    outside, depth = [], 0
+    for line in hooks.splitlines():
+        if line.startswith("#if"):
+            depth += 1
+        elif line.startswith("#endif"):
+            depth -= 1
+        elif depth == 0 or line.startswith("#else"):
+            outside.append(line)
+    assert not any("nvtxRange" in l or "cudaProfilerStart" in l for l in outside if not l.lstrip().startswith("//"))
+    build = _text(PKG / "_build.py")
+    assert "-DNANO_NCCL_ENABLE_BENCH_PROFILING" not in build
+
+
+def test_mpi_is_used_through_its_c_interface_only():
+    """mpi_c_api_link_static.py: no C++ MPI bindings anywhere; the bundled mpi.h declares a C interface."""
+    for p in NATIVE:
+        t = _text(p)
+        assert "MPI::" not in t and "mpicxx.h" not in t, p
+    assert 'extern "C"' in _text(PKG / "csrc" / "minimpi" / "mpi.h")
+
+
+def test_rdma_receive_orders_poll_flush_size_tail():
+    """rdma_proxy_gdr_receive_flush_static.py: completion polled -> GPUDirect flush -> slot size -> tail published."""
+    src = _text(PKG / "csrc" / "transport" / "rdma" / "rdma_proxy.cc")
+    recv = src[src.index("// ---- completions: flush"):]
+    _in_order(recv, ["qp_->poll(", "flush_.flush(", "fifo_.slot_bytes[", "host_store_step(fifo_.tail"])
+
+
+def test_rdma_send_is_selectively_signalled_from_the_registered_fifo():
+    """rdma_proxy_multi_flight_static.py, rdma_proxy_send_visibility_static.py, rdma_transport_static.py: several
+    sends in flight, a completion asked for every few posts / at a burst's end / before a zero slice, the payload
+    posted straight from the registered FIFO (no host bounce copy), queue pairs created unsignalled."""
+    src = _text(PKG / "csrc" / "transport" / "rdma" / "rdma_proxy.cc")
+    assert re.search(r"signaled = !more \|\| next_is_zero \|\| \(posts_ % kSignalEvery\)", src)
+    send = src[:src.index("// ---- completions: flush")]
+    assert "memcpy" not in send, "the send path copies the payload on the host"
+    ibv = _text(PKG / "csrc" / "transport" / "rdma" / "verbs_ibv.cc")
+    assert "init.sq_sig_all = 0;" in ibv and "kMaxInline = 64" in ibv
+    _in_order(ibv, ["IBV_QPS_INIT", "IBV_QPS_RTR", "min_rnr_timer = 12", "IBV_QPS_RTS", "timeout = 14", "retry_cnt = 7"])
+
+
+def test_rdma_cts_is_inline_when_it_fits_and_zero_slices_post_nothing():
+    """rdma_proxy_write_cts_static.py, rdma_proxy_zero_byte_static.py."""
+    src = _text(PKG / "csrc" / "transport" / "rdma" / "rdma_proxy.cc")
+    assert "sizeof(RdmaCtsSlot) <= qp_->max_inline()" in src
+    assert re.search(r"zero", src) and "zero_payload" in _text(PKG / "csrc" / "transport" / "rdma" / "rdma_proxy.h")
+    proto = _text(PKG / "csrc" / "transport" / "rdma" / "rdma_protocol.h")
+    assert "sizeof(RdmaPeerInfo) == 72" in proto and "sizeof(RdmaCtsSlot) == 32" in proto
+
+
+def test_gpu_memory_registration_never_falls_back_to_host_memory():
+    """rdma_gdr_static.py: synchronous memory operations on the range, dma-buf first, then peer memory, then an error."""
+    ibv = _text(PKG / "csrc" / "transport" / "rdma" / "verbs_ibv.cc")
+    body = _body(ibv, "std::unique_ptr<MemoryRegion> register_device(")
+    _in_order(body, ["CU_POINTER_ATTRIBUTE_SYNC_MEMOPS", "cuMemGetHandleForAddressRange", "reg_dmabuf", "api.reg_mr(", "fail("])
+    assert "register_host" not in body
+
+
+def test_simple_protocol_counters_have_one_writer_each():
+    """simple_protocol_ownership_static.py: head (credit) is written by the receiver, tail (data ready) by the sender,
+    both with system-scope release stores and read with acquire loads."""
+    step = _text(PKG / "csrc" / "transport" / "simple" / "step.h")
+    assert "st.release.sys" in step and "ld.acquire.sys" in step
+    ring = _text(PKG / "csrc" / "kernels" / "ring_simple.cuh")
+    assert re.search(r"store_step\([^;]*tail", ring) and re.search(r"store_step\([^;]*head", ring)

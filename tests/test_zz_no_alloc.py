@@ -41,16 +41,28 @@ def test_noalloc_matches_allocating_entry_point_twice_in_a_row():
     try:
         # call 1: bf16 sum, a size that needs several tiles; call 2: fp32 max with another size,
         # straight after, on the scratch that call 1 left behind
+        # call 3 repeats call 2's variant: by then the driver has loaded that kernel, so the free device memory
+        # must not move at all across the call (this also sees allocations that bypass torch's allocator)
+        status_fn = lib.nano_nccl_all_reduce_local_noalloc_status
+        status_fn.restype = C.c_int32
+        status_fn.argtypes = [C.c_void_p, C.POINTER(C.c_uint32)]
         for call, (dtype, op, count, nranks) in enumerate([(torch.bfloat16, "sum", 300_003, 4),
-                                                           (torch.float32, "max", 70_001, 4)]):
+                                                           (torch.float32, "max", 70_001, 4),
+                                                           (torch.float32, "max", 65_537, 4)]):
             g = torch.Generator().manual_seed(17 + call)
             xs = [(torch.rand(count, generator=g) * 2 - 1).to(dtype).cuda() for _ in range(nranks)]
             got = [torch.full((count,), -9137.25, dtype=dtype, device="cuda") for _ in range(nranks)]
             want = [torch.empty(count, dtype=dtype, device="cuda") for _ in range(nranks)]
+            torch.cuda.synchronize()
             before = torch.cuda.memory_allocated()
+            free_before = torch.cuda.mem_get_info()[0]
             rc = fn(_ptrs(xs), _ptrs(got), nranks, count, DT[dtype], N.REDOPS[op], stream)
             assert rc == 0, lib.nano_nccl_get_last_error()
+            words = (C.c_uint32 * 4)()
+            assert status_fn(stream, words) == 0 and list(words) == [0, 0, 0, 0], (list(words), lib.nano_nccl_get_last_error())
             assert torch.cuda.memory_allocated() == before  # nothing taken from torch's allocator either
+            if call == 2:
+                assert torch.cuda.mem_get_info()[0] >= free_before, "device memory was allocated behind torch's back"
             N.check(lib.nano_nccl_emu_all_reduce(emu, _ptrs(xs), _ptrs(want), count, DT[dtype], N.REDOPS[op],
                                                  N.ALGOS["oneshot"], 8, stream))
             torch.cuda.synchronize()

@@ -1,12 +1,13 @@
-"""Checks of kernels that are built but not yet part of the GPU test suite, runnable by hand on one GPU:
+"""Single-GPU checks of kernel variants that are selected by an environment variable or a run-time argument
+(each case is one process, so the variable is set before the library reads it):
 
-    python tests/workers/experimental_checks.py bulk_copy        # TMA bulk-copy and vector-copy push kernels, local
-    python tests/workers/experimental_checks.py emu_tma_allgather # AllGather with TMA pushes, 2 / 4 / 8 emulated ranks
-    python tests/workers/experimental_checks.py emu_ll            # flag-in-data small-message kernels, emulated ranks
-    python tests/workers/experimental_checks.py fused_single      # GEMM / fused kernels with one rank and every tile width
+    bulk_copy          TMA bulk-copy, vector-copy and copy-engine push kernels, local destinations
+    emu_tma_allgather  AllGather whose pushes are TMA bulk copies (NANO_NCCL_PUSH_TMA=1), 2 / 4 / 8 emulated ranks
+    emu_ll             flag-in-data small-message kernels (NANO_NCCL_LL_MAX_BYTES), 2 / 4 / 8 emulated ranks
+    fused_single       plain GEMM and the fused GEMM kernels with one rank and every tile width
 
-Each check compares against a plain PyTorch result, uses guard bands, and relies on the kernels' bounded
-waits; a case moves into tests/ once it has passed on a GPU.
+Each check compares against a plain PyTorch result, uses guard bands, and relies on the kernels' bounded waits.
+tests/test_gpu_variants.py runs them.
 """
 import ctypes as C
 import os
