@@ -44,7 +44,7 @@ class ExtConfig(C.Structure):
 
 class Stats(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in
-                ("launches", "oneshot", "twoshot", "nvls", "ring", "zero_copy", "local_only")]
+                ("launches", "oneshot", "twoshot", "nvls", "ring", "zero_copy", "local_only", "pipelined")]
 
 
 class MpiSubgroupConfig(C.Structure):

@@ -389,7 +389,7 @@ nano_nccl_status_t nano_nccl_get_stats(const nano_nccl_communicator_t* communica
     if (auto s = require_handle(communicator)) return s;
     if (stats == nullptr) return fail(NANO_NCCL_STATUS_INVALID_ARGUMENT, "stats must be non-null");
     const CommunicatorStats st = communicator->communicator->stats();
-    *stats = nano_nccl_stats_t{st.launches, st.oneshot, st.twoshot, st.nvls, st.ring, st.zero_copy, st.local_only};
+    *stats = nano_nccl_stats_t{st.launches, st.oneshot, st.twoshot, st.nvls, st.ring, st.zero_copy, st.local_only, st.pipelined};
     return NANO_NCCL_STATUS_SUCCESS;
 }
 

@@ -134,6 +134,14 @@ Communicator::Impl::Impl(std::shared_ptr<Bootstrap> bootstrap, const Communicato
         debug_level_ = *level == "info" ? 1 : *level == "trace" ? 2 : 0;
     }
     push_tma_ = env::flag("NANO_NCCL_PUSH_TMA", false);
+    // Messages of at least this many bytes (AllReduce message; ReduceScatter / AllGather: the whole N-chunk buffer)
+    // take the software-pipelined kernels; 0 switches them off.
+    pipe_min_bytes_ = static_cast<std::size_t>(env::integer("NANO_NCCL_PIPE_MIN_BYTES", 8 << 20, 0, 1ll << 40));
+    pipe_tile_bytes_ = static_cast<std::size_t>(env::integer("NANO_NCCL_PIPE_TILE_BYTES", 0, 0, 1 << 20));
+    if (auto algo = env::get("NANO_NCCL_PIPE_ALGO")) {
+        NANO_REQUIRE_ARG(parse_algo(algo->c_str(), &pipe_algo_) && (pipe_algo_ == AlgoKind::Auto || pipe_algo_ == AlgoKind::TwoShot || pipe_algo_ == AlgoKind::Nvls),
+                         "NANO_NCCL_PIPE_ALGO must be auto, twoshot or nvls, got '%s'", algo->c_str());
+    }
     tile_cap_ = static_cast<std::size_t>(env::integer("NANO_NCCL_TILE_BYTES", 0, 0, 1 << 20));
 
     // 6. NVLink data plane: symmetric arena + signal pads when every edge is GPU peer-to-peer
@@ -396,6 +404,27 @@ void Communicator::Impl::all_reduce(const AllReduceArgs& a) {
         CUDA_CHECK_THROW(err);
         return;
     }
+    const bool adds = a.redop == RedOp::Sum || a.redop == RedOp::Avg;
+    if (pipe_min_bytes_ != 0 && bytes >= pipe_min_bytes_ && d.algo != AlgoKind::OneShot) {
+        // Large message: the software-pipelined kernels.  Through the switch when it can add (both link directions
+        // carry about one message each); otherwise, and on two ranks, the two-shot form over peer stores.
+        const bool through_switch = multicast_available() && adds &&
+                                    (pipe_algo_ == AlgoKind::Nvls || (pipe_algo_ == AlgoKind::Auto && (nranks_ > 2 || d.algo == AlgoKind::Nvls)));
+        if (through_switch) {
+            const dev::Geometry g = dev::make_pipe_geometry(dev::Family::ArNvls, a.count, dtype_size(a.dtype), nranks_, d.max_grid, pipe_tile_bytes_);
+            err = dev::launch_ar_nvls_pipe(dev_, a.send_buffer, a.recv_buffer, a.count, a.dtype, a.redop, g, a.stream);
+            ++stats_.nvls;
+            last_algo_ = AlgoKind::Nvls;
+        } else {
+            const dev::Geometry g = dev::make_pipe_geometry(dev::Family::ArTwoShot, a.count, dtype_size(a.dtype), nranks_, d.max_grid, pipe_tile_bytes_);
+            err = dev::launch_ar_twoshot_pipe(dev_, a.send_buffer, a.recv_buffer, a.count, a.dtype, a.redop, push_multicast(), g, a.stream);
+            ++stats_.twoshot;
+            last_algo_ = AlgoKind::TwoShot;
+        }
+        ++stats_.pipelined;
+        CUDA_CHECK_THROW(err);
+        return;
+    }
     if (d.algo == AlgoKind::Nvls) {
         const dev::Geometry g = dev::make_geometry(dev::Family::ArNvls, a.count, dtype_size(a.dtype), nranks_, d.max_grid, skew_, tile_cap_);
         err = dev::launch_ar_nvls(dev_, a.send_buffer, a.recv_buffer, a.count, a.dtype, a.redop, g, a.stream);
@@ -473,6 +502,15 @@ void Communicator::Impl::reduce_scatter(const ReduceScatterArgs& a) {
         CUDA_CHECK_THROW(e);
         return;
     }
+    if (pipe_min_bytes_ != 0 && bytes * nranks_ >= pipe_min_bytes_) {
+        const dev::Geometry g = dev::make_pipe_geometry(dev::Family::ReduceScatter, a.recv_count, dtype_size(a.dtype), nranks_, d.max_grid, pipe_tile_bytes_);
+        const cudaError_t e = dev::launch_rs_pipe(dev_, a.send_buffer, a.recv_buffer, a.recv_count, a.dtype, a.redop, g, a.stream);
+        ++stats_.oneshot;
+        ++stats_.pipelined;
+        last_algo_ = AlgoKind::OneShot;
+        CUDA_CHECK_THROW(e);
+        return;
+    }
     const dev::Geometry g = dev::make_geometry(dev::Family::ReduceScatter, a.recv_count, dtype_size(a.dtype), nranks_, d.max_grid, false, tile_cap_);
     const cudaError_t err = dev::launch_rs_push(dev_, a.send_buffer, a.recv_buffer, a.recv_count, a.dtype, a.redop, g, a.stream);
     ++stats_.oneshot;
@@ -527,6 +565,15 @@ void Communicator::Impl::all_gather(const AllGatherArgs& a) {
         const cudaError_t e = dev::launch_ag_ll(dev_, ll_dev_, a.send_buffer, a.recv_buffer, a.send_count, a.dtype,
                                                 push_multicast() && ll_dev_.stage_mc != nullptr, g, a.stream);
         ++stats_.oneshot;
+        last_algo_ = AlgoKind::OneShot;
+        CUDA_CHECK_THROW(e);
+        return;
+    }
+    if (pipe_min_bytes_ != 0 && bytes * nranks_ >= pipe_min_bytes_ && !push_tma_) {
+        const dev::Geometry g = dev::make_pipe_geometry(dev::Family::AllGather, a.send_count, dtype_size(a.dtype), nranks_, d.max_grid, pipe_tile_bytes_);
+        const cudaError_t e = dev::launch_ag_pipe(dev_, a.send_buffer, a.recv_buffer, a.send_count, a.dtype, push_multicast(), g, a.stream);
+        ++stats_.oneshot;
+        ++stats_.pipelined;
         last_algo_ = AlgoKind::OneShot;
         CUDA_CHECK_THROW(e);
         return;

@@ -66,6 +66,7 @@ struct CommunicatorStats {
     std::uint64_t ring = 0;
     std::uint64_t zero_copy = 0;  // collectives that ran without staging copies
     std::uint64_t local_only = 0; // single-rank degenerate copies
+    std::uint64_t pipelined = 0;  // collectives that took the software-pipelined large-message kernels
 };
 
 namespace collective {

@@ -70,7 +70,7 @@ nano_nccl_status_t nano_nccl_multicast_pointer(const nano_nccl_communicator_t* c
 nano_nccl_status_t nano_nccl_barrier(nano_nccl_communicator_t* communicator, cudaStream_t stream);
 
 typedef struct NanoNcclStats {
-    uint64_t launches, oneshot, twoshot, nvls, ring, zero_copy, local_only;
+    uint64_t launches, oneshot, twoshot, nvls, ring, zero_copy, local_only, pipelined;
 } nano_nccl_stats_t;
 nano_nccl_status_t nano_nccl_get_stats(const nano_nccl_communicator_t* communicator,
                                        nano_nccl_stats_t* stats);

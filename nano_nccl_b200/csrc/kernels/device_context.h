@@ -44,6 +44,7 @@ enum StatusCode : std::uint32_t {
 struct BlockState {
     std::uint32_t epoch;  // value of the last barrier this block completed
     std::uint32_t seq;    // launches this block took part in (staging half = seq & 1)
+    std::uint32_t epoch_b;  // second signal counter of the pipelined kernels (kernels/pipelined.cuh)
 };
 
 struct CommDev {

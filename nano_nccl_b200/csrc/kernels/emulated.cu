@@ -6,6 +6,7 @@
 #include "core/error.h"
 #include "kernels/dispatch.cuh"
 #include "kernels/ll_collectives.cuh"
+#include "kernels/pipelined.cuh"
 
 #include <vector>
 
@@ -22,6 +23,9 @@ struct EmulatedCluster::State {
     std::vector<RawDeviceBuffer> ll_arenas;
     RawDeviceBuffer ll_dev;     // LLDev
     std::size_t ll_max_bytes = 0;
+    // software-pipelined kernels for messages of at least this size (NANO_NCCL_PIPE_MIN_BYTES when the cluster is created)
+    std::size_t pipe_min_bytes = 0;
+    std::size_t pipe_tile_bytes = 0;
 };
 
 namespace {
@@ -83,6 +87,8 @@ EmulatedCluster::EmulatedCluster(int device, int nranks, std::int64_t timeout_us
     }
     s_->ranks_dev = RawDeviceBuffer(device, sizeof(EmuRanks));
     s_->ll_max_bytes = static_cast<std::size_t>(env::integer("NANO_NCCL_LL_MAX_BYTES", 0, 0, 16 << 20));
+    s_->pipe_min_bytes = static_cast<std::size_t>(env::integer("NANO_NCCL_PIPE_MIN_BYTES", 8 << 20, 0, 1ll << 40));
+    s_->pipe_tile_bytes = static_cast<std::size_t>(env::integer("NANO_NCCL_PIPE_TILE_BYTES", 0, 0, 1 << 20));
     if (s_->ll_max_bytes != 0) {
         LLDev l{};
         for (int r = 0; r < nranks; ++r) {
@@ -118,7 +124,9 @@ void EmulatedCluster::all_reduce(const void* const* srcs, void* const* dsts, std
     upload(s_->ranks_host, s_->ranks_dev, srcs, dsts, nranks_, stream);
     const Family fam = algo == AlgoKind::OneShot ? Family::ArOneShot : Family::ArTwoShot;
     const bool ll = algo == AlgoKind::OneShot && s_->ll_max_bytes != 0 && count * dtype_size(dtype) <= s_->ll_max_bytes;
-    const Geometry g = make_geometry(fam, count, dtype_size(dtype), nranks_, max_grid, !ll, ll ? ll_tile_cap_bytes(nranks_) : 0);
+    const bool pipe = algo == AlgoKind::TwoShot && s_->pipe_min_bytes != 0 && count * dtype_size(dtype) >= s_->pipe_min_bytes;
+    const Geometry g = pipe ? make_pipe_geometry(fam, count, dtype_size(dtype), nranks_, max_grid, s_->pipe_tile_bytes)
+                            : make_geometry(fam, count, dtype_size(dtype), nranks_, max_grid, !ll, ll ? ll_tile_cap_bytes(nranks_) : 0);
     const EmuRanks* e = static_cast<const EmuRanks*>(s_->ranks_dev.data());
     const LLDev* l = static_cast<const LLDev*>(s_->ll_dev.data());
     const dim3 grid(g.grid, nranks_);
@@ -126,7 +134,9 @@ void EmulatedCluster::all_reduce(const void* const* srcs, void* const* dsts, std
         using T = decltype(t);
         return dispatch_op(op, [&](auto o) {
             constexpr RedOp Op = decltype(o)::value;
-            if (ll) {
+            if (pipe) {
+                launch_cooperative(ar_twoshot_pipe_emu_kernel<T, Op>, grid, stream, e, count, g);
+            } else if (ll) {
                 launch_cooperative(ar_oneshot_ll_emu_kernel<T, Op>, grid, stream, e, l, count, g);
             } else if (algo == AlgoKind::OneShot) {
                 launch_cooperative(ar_oneshot_emu_kernel<T, Op>, grid, stream, e, count, g);
@@ -143,8 +153,10 @@ void EmulatedCluster::reduce_scatter(const void* const* srcs, void* const* dsts,
     CUDA_CHECK_THROW(cudaSetDevice(device_));
     upload(s_->ranks_host, s_->ranks_dev, srcs, dsts, nranks_, stream);
     const bool ll = s_->ll_max_bytes != 0 && recv_count * dtype_size(dtype) * nranks_ <= s_->ll_max_bytes;
-    const Geometry g = make_geometry(Family::ReduceScatter, recv_count, dtype_size(dtype), nranks_, max_grid, true,
-                                     ll ? ll_tile_cap_bytes(nranks_) : 0);
+    const bool pipe = s_->pipe_min_bytes != 0 && recv_count * dtype_size(dtype) * nranks_ >= s_->pipe_min_bytes;
+    const Geometry g = pipe ? make_pipe_geometry(Family::ReduceScatter, recv_count, dtype_size(dtype), nranks_, max_grid, s_->pipe_tile_bytes)
+                            : make_geometry(Family::ReduceScatter, recv_count, dtype_size(dtype), nranks_, max_grid, true,
+                                            ll ? ll_tile_cap_bytes(nranks_) : 0);
     const EmuRanks* e = static_cast<const EmuRanks*>(s_->ranks_dev.data());
     const LLDev* l = static_cast<const LLDev*>(s_->ll_dev.data());
     const dim3 grid(g.grid, nranks_);
@@ -152,7 +164,8 @@ void EmulatedCluster::reduce_scatter(const void* const* srcs, void* const* dsts,
         using T = decltype(t);
         return dispatch_op(op, [&](auto o) {
             constexpr RedOp Op = decltype(o)::value;
-            if (ll) launch_cooperative(rs_ll_emu_kernel<T, Op>, grid, stream, e, l, recv_count, g);
+            if (pipe) launch_cooperative(rs_pipe_emu_kernel<T, Op>, grid, stream, e, recv_count, g);
+            else if (ll) launch_cooperative(rs_ll_emu_kernel<T, Op>, grid, stream, e, l, recv_count, g);
             else launch_cooperative(rs_push_emu_kernel<T, Op>, grid, stream, e, recv_count, g);
             return cudaGetLastError();
         });
@@ -164,10 +177,19 @@ void EmulatedCluster::all_gather(const void* const* srcs, void* const* dsts, std
     CUDA_CHECK_THROW(cudaSetDevice(device_));
     upload(s_->ranks_host, s_->ranks_dev, srcs, dsts, nranks_, stream);
     const bool ll = s_->ll_max_bytes != 0 && send_count * dtype_size(dtype) * nranks_ <= s_->ll_max_bytes;
-    const Geometry g = make_geometry(Family::AllGather, send_count, dtype_size(dtype), nranks_, max_grid, true,
-                                     ll ? ll_tile_cap_bytes(nranks_) : 0);
+    const bool pipe = s_->pipe_min_bytes != 0 && send_count * dtype_size(dtype) * nranks_ >= s_->pipe_min_bytes &&
+                      !env::flag("NANO_NCCL_PUSH_TMA", false);
+    const Geometry g = pipe ? make_pipe_geometry(Family::AllGather, send_count, dtype_size(dtype), nranks_, max_grid, s_->pipe_tile_bytes)
+                            : make_geometry(Family::AllGather, send_count, dtype_size(dtype), nranks_, max_grid, true,
+                                            ll ? ll_tile_cap_bytes(nranks_) : 0);
     const EmuRanks* e = static_cast<const EmuRanks*>(s_->ranks_dev.data());
     const dim3 grid(g.grid, nranks_);
+    if (pipe) {
+        if (dtype == DType::Float) launch_cooperative(ag_pipe_emu_kernel<float>, grid, stream, e, send_count, g);
+        else launch_cooperative(ag_pipe_emu_kernel<__half>, grid, stream, e, send_count, g);
+        CUDA_CHECK_THROW(cudaGetLastError());
+        return;
+    }
     if (ll) {
         const LLDev* l = static_cast<const LLDev*>(s_->ll_dev.data());
         if (dtype == DType::Float) launch_cooperative(ag_ll_emu_kernel<float>, grid, stream, e, l, send_count, g);

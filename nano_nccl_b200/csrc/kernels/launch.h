@@ -108,6 +108,19 @@ cudaError_t launch_ag_ll(const CommDev& c, const LLDev& l, const void* src, void
                          DType dtype, bool multicast, const Geometry& g, cudaStream_t stream);
 cudaError_t launch_barrier(const CommDev& c, int grid, cudaStream_t stream);
 
+// Software-pipelined forms for large messages (kernels/pipelined.cuh): a CTA keeps three tiles in flight and
+// waits only for signals that are one iteration old.  `g` must come from make_pipe_geometry.
+Geometry make_pipe_geometry(Family family, std::size_t count, std::size_t elem_size, int nranks, int max_grid,
+                            std::size_t tile_bytes_hint = 0);
+cudaError_t launch_ar_twoshot_pipe(const CommDev& c, const void* src, void* dst, std::size_t count, DType dtype, RedOp op,
+                                   bool multicast, const Geometry& g, cudaStream_t stream);
+cudaError_t launch_ar_nvls_pipe(const CommDev& c, const void* src, void* dst, std::size_t count, DType dtype, RedOp op,
+                                const Geometry& g, cudaStream_t stream);
+cudaError_t launch_rs_pipe(const CommDev& c, const void* src, void* dst, std::size_t recv_count, DType dtype, RedOp op,
+                           const Geometry& g, cudaStream_t stream);
+cudaError_t launch_ag_pipe(const CommDev& c, const void* src, void* dst, std::size_t send_count, DType dtype,
+                           bool multicast, const Geometry& g, cudaStream_t stream);
+
 // Copies `bytes` (a multiple of 16) from `src` to each of `ndst` destinations, all 16-byte aligned, with
 // untiled TMA bulk copies through `stages` (3..16) shared-memory stages of `chunk_bytes` per CTA
 // (kernels/bulk_copy.cu).  `device_error` is a zeroed device word that becomes 1 if a wait ran out.

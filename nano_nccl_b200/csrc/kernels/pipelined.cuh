@@ -1,0 +1,390 @@
+// Software-pipelined forms of the NVLink collective kernels for large messages.
+//
+// The plain kernels (collectives.cuh) run a tile through its phases one after the other: push, barrier,
+// reduce / broadcast, barrier, copy out.  With a large message every CTA of every GPU is in the same phase
+// at the same time, so NVLink is busy during the pushes and idle during the local copies, and every
+// barrier exposes a release fence plus a flag flight.  Here a CTA works on three tiles at once, one per
+// stage, and only ever waits for a signal that its peers sent one iteration earlier:
+//
+//   iteration k:   A(k)    push tile k                                   signal A(k)
+//                  C(k-2)  [wait B(k-2)]  copy tile k-2 out               (three-stage kernels)
+//                  B(k-1)  [wait A(k-1)]  reduce / broadcast tile k-1    signal B(k-1)
+//
+// Tile k lives in staging buffer k mod 3 of the CTA (three buffers of kPipeBufBytes inside the CTA's
+// 2 MiB of staging).  Why three are enough: buffer k mod 3 is written again by the peers' A(k+3), which
+// they start after their iteration k+2, and that iteration waited for B(k) of every rank; what B writes
+// (the gather area) is written again by the peers' B(k+3) after they waited for A(k+3), which a rank
+// signals after its C(k).  Two-stage kernels (ReduceScatter, AllGather) wait for B(k-3) before A(k).
+//
+// Signals are two monotonic counters per (CTA, peer): stream A in the ordinary pad row (the same words and
+// the same epoch counter as block_barrier, of which a signal is one half), stream B in a second row.
+// A kernel starts and ends with a full barrier, because the plain kernels index the same staging bytes by
+// halves: the first keeps the pushes away from a peer that is still copying out of the previous kernel's
+// half, the last lets the next kernel write anywhere.  All waits are bounded like everywhere else.
+//
+// The reference pipelines its ring the same way in spirit (up to four slices in flight per edge:
+// src/kernels/ring_simple_kernel.cuh:1116-1438); this is that idea on one- and two-hop algorithms.
+#pragma once
+
+#include "kernels/collectives.cuh"
+
+namespace nano_nccl::dev {
+
+constexpr int kPipeDepth = 3;
+constexpr std::size_t kPipeBufBytes = 640 * 1024;
+static_assert(kPipeDepth * kPipeBufBytes <= kBlockStageBytes, "three pipeline buffers fit a CTA's staging");
+// Second flag row: word index of (block, rank) inside a rank's signal pads.  Below the fused-GEMM flags.
+constexpr std::size_t kPipeFlagRowWords = 2048;
+static_assert((kPipeFlagRowWords + kMaxBlocks * kPadWordsPerBlock) * 4 <= kGemmFlagOffsetBytes, "second flag row fits");
+
+__device__ __forceinline__ std::size_t pipe_buf_offset(int k) {
+    return static_cast<std::size_t>(blockIdx.x) * kBlockStageBytes + static_cast<std::size_t>(k % kPipeDepth) * kPipeBufBytes;
+}
+
+// Threads 0..N-1 store `value` into the flag word (row, this block, this rank) of their peer.  The caller has
+// just passed a __syncthreads, so the release covers everything the block wrote before it.
+__device__ __forceinline__ void pipe_signal(const CommDev& c, std::size_t row, std::uint32_t value) {
+    const int peer = static_cast<int>(threadIdx.x);
+    if (peer < c.nranks && peer != c.rank) {
+        st_release_sys(c.pad[peer] + row + blockIdx.x * kPadWordsPerBlock + c.rank, value);
+    }
+}
+
+// Waits until every peer's flag word (row, this block) has reached `target`; uniform result over the block.
+__device__ __forceinline__ bool pipe_wait(const CommDev& c, std::size_t row, std::uint32_t target, int phase,
+                                          volatile std::uint32_t* giveup) {
+    int ok = 1;
+    const int peer = static_cast<int>(threadIdx.x);
+    if (peer < c.nranks && peer != c.rank) {
+        ok = wait_flag(c, c.pad[c.rank] + row + blockIdx.x * kPadWordsPerBlock + peer, target, peer, phase, giveup,
+                       peer == (c.rank == 0 ? 1 : 0)) ? 1 : 0;
+    }
+    return __syncthreads_and(ok) != 0;
+}
+
+// The schedule.  stage_a / stage_b / stage_c take the tile index; kThree selects the three-stage form.
+template <bool kThree, typename FA, typename FB, typename FC>
+__device__ __forceinline__ void pipe_run(const CommDev& c, int tiles, FA&& stage_a, FB&& stage_b, FC&& stage_c) {
+    __shared__ std::uint32_t giveup;
+    std::uint32_t epoch = c.state[blockIdx.x].epoch;
+    std::uint32_t epoch_b = c.state[blockIdx.x].epoch_b;
+    const std::uint32_t seq = c.state[blockIdx.x].seq;
+    if (threadIdx.x == 0) giveup = 0u;
+    bool ok = block_barrier(c, epoch, 1);
+    const std::uint32_t a0 = epoch, b0 = epoch_b;  // signal A(k) carries a0 + k + 1, signal B(k) carries b0 + k + 1
+    const int last = tiles + (kThree ? 1 : 0);
+    for (int k = 0; ok && k <= last; ++k) {
+        if (k < tiles) {
+            if (!kThree && k >= kPipeDepth) {
+                ok = pipe_wait(c, kPipeFlagRowWords, b0 + static_cast<std::uint32_t>(k - kPipeDepth) + 1u, 3, &giveup);
+                if (!ok) break;
+            }
+            stage_a(k);
+            __syncthreads();
+            pipe_signal(c, 0, a0 + static_cast<std::uint32_t>(k) + 1u);
+        }
+        if (kThree && k >= 2 && k - 2 < tiles) {
+            ok = pipe_wait(c, kPipeFlagRowWords, b0 + static_cast<std::uint32_t>(k - 2) + 1u, 4, &giveup);
+            if (!ok) break;
+            stage_c(k - 2);
+        }
+        if (k >= 1 && k - 1 < tiles) {
+            ok = pipe_wait(c, 0, a0 + static_cast<std::uint32_t>(k), 3, &giveup);
+            if (!ok) break;
+            stage_b(k - 1);
+            __syncthreads();
+            pipe_signal(c, kPipeFlagRowWords, b0 + static_cast<std::uint32_t>(k));
+        }
+    }
+    if (ok) {
+        epoch = a0 + static_cast<std::uint32_t>(tiles);
+        epoch_b = b0 + static_cast<std::uint32_t>(tiles);
+        block_barrier(c, epoch, 2);
+    }
+    if (threadIdx.x == 0) {
+        c.state[blockIdx.x].epoch = epoch;
+        c.state[blockIdx.x].epoch_b = epoch_b;
+        c.state[blockIdx.x].seq = seq;
+    }
+}
+
+// Copies `nvec` 16-byte vectors with kPipeBatch loads in flight per thread.  LoadFn(v) -> Vec16, StoreFn(v, x).
+// Four per thread (2048 per CTA, 32 KiB) cover the bandwidth-delay product of a CTA's share of NVLink several
+// times over and leave the three inlined stages enough registers under the 128-register cap of a 512-thread CTA.
+constexpr int kPipeBatch = 4;
+template <typename LoadFn, typename StoreFn>
+__device__ __forceinline__ void batched_copy(std::size_t nvec, LoadFn&& load, StoreFn&& store) {
+    for (std::size_t v0 = threadIdx.x; v0 < nvec; v0 += kPipeBatch * blockDim.x) {
+        Vec16 x[kPipeBatch];
+#pragma unroll
+        for (int k = 0; k < kPipeBatch; ++k) {
+            const std::size_t v = v0 + k * blockDim.x;
+            if (v < nvec) x[k] = load(v);
+        }
+#pragma unroll
+        for (int k = 0; k < kPipeBatch; ++k) {
+            const std::size_t v = v0 + k * blockDim.x;
+            if (v < nvec) store(v, x[k]);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Two-shot AllReduce, pipelined.  A buffer is split into a scatter half and a gather half of N slots each;
+// g.slot_bytes = bytes of one rank's sub-slice of a tile.
+template <typename T, RedOp Op, bool kMc>
+__device__ __forceinline__ void
+ar_twoshot_pipe_body(const CommDev& c, const T* src, T* dst, std::size_t count, const Geometry g) {
+    constexpr int kE = ElemsPerVec<T>::value;
+    constexpr std::size_t kGatherOff = kPipeBufBytes / 2;
+    const float inv = 1.0f / static_cast<float>(c.nranks);
+    const int N = c.nranks;
+    auto tile = [&](int k, std::size_t* t0, std::size_t* n) { tile_range(count, g, k, t0, n); };
+    auto stage_a = [&](int k) {  // sub-slice j of my tile goes to rank j
+        std::size_t t0, n;
+        tile(k, &t0, &n);
+        if (!tile_fits(c, max_split_bytes<T>(n, N), g.slot_bytes, N, kGatherOff)) return;
+        const std::size_t off = pipe_buf_offset(k);
+        const T* s = src + t0;
+        const bool s_al = aligned16(s);
+        for (int i = 1; i < N; ++i) {
+            const int j = (c.rank + i) % N;
+            const std::size_t b = split_begin(n, N, j, kE), e = split_begin(n, N, j + 1, kE);
+            const std::size_t len = e - b;
+            char* out = c.stage[j] + off + c.rank * g.slot_bytes;
+            batched_copy((len + kE - 1) / kE, [&](std::size_t v) { return load_guarded(s + b, v * kE, len, s_al); },
+                         [&](std::size_t v, const Vec16& x) { st_vec(out + v * 16, x); });
+        }
+    };
+    auto stage_b = [&](int k) {  // reduce my sub-slice in rank order, write it to my output and to everyone's gather half
+        std::size_t t0, n;
+        tile(k, &t0, &n);
+        if (!tile_fits(c, max_split_bytes<T>(n, N), g.slot_bytes, N, kGatherOff)) return;
+        const std::size_t off = pipe_buf_offset(k);
+        const T* s = src + t0;
+        T* d = dst + t0;
+        const bool s_al = aligned16(s), d_al = aligned16(d);
+        const std::size_t b = split_begin(n, N, c.rank, kE), e = split_begin(n, N, c.rank + 1, kE);
+        const std::size_t len = e - b, nvec = (len + kE - 1) / kE;
+        const char* in = c.stage[c.rank] + off;
+        const std::size_t go = off + kGatherOff + c.rank * g.slot_bytes;
+        for (std::size_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+            Acc<T> acc;
+            for (int r = 0; r < N; ++r) {
+                const Vec16 x = (r == c.rank) ? load_guarded(s + b, v * kE, len, s_al)
+                                              : ld_vec_volatile(in + r * g.slot_bytes + v * 16);
+                if (r == 0) acc = unpack<T>(x); else combine<Op, T>(acc, unpack<T>(x));
+            }
+            finish<Op, T>(acc, inv);
+            const Vec16 y = pack<T>(acc);
+            store_guarded(d + b, v * kE, len, d_al, y);
+            if constexpr (kMc) {
+                multimem_st(c.stage_mc + go + v * 16, y);
+            } else {
+                for (int i = 1; i < N; ++i) st_vec(c.stage[(c.rank + i) % N] + go + v * 16, y);
+            }
+        }
+    };
+    auto stage_c = [&](int k) {  // the other owners' results leave my gather half
+        std::size_t t0, n;
+        tile(k, &t0, &n);
+        const std::size_t off = pipe_buf_offset(k);
+        T* d = dst + t0;
+        const bool d_al = aligned16(d);
+        for (int i = 1; i < N; ++i) {
+            const int j = (c.rank + i) % N;
+            const std::size_t b = split_begin(n, N, j, kE), e = split_begin(n, N, j + 1, kE);
+            const std::size_t len = e - b;
+            const char* in = c.stage[c.rank] + off + kGatherOff + j * g.slot_bytes;
+            batched_copy((len + kE - 1) / kE, [&](std::size_t v) { return ld_vec_volatile(in + v * 16); },
+                         [&](std::size_t v, const Vec16& x) { store_guarded(d + b, v * kE, len, d_al, x); });
+        }
+    };
+    pipe_run<true>(c, g.iters, stage_a, stage_b, stage_c);
+}
+
+// ------------------------------------------------------------------------------------------------
+// AllReduce through the switch, pipelined: A copies the tile into the multicast-bound buffer, B reduces the
+// owned slice in the switch and writes the result into every rank's buffer, C copies the rest out.
+template <typename T, RedOp Op>
+__device__ __forceinline__ void
+ar_nvls_pipe_body(const CommDev& c, const T* src, T* dst, std::size_t count, const Geometry g) {
+    static_assert(Op == RedOp::Sum || Op == RedOp::Avg, "the switch only adds");
+    constexpr int kE = ElemsPerVec<T>::value;
+    const float inv = 1.0f / static_cast<float>(c.nranks);
+    const int N = c.nranks;
+    auto stage_a = [&](int k) {
+        std::size_t t0, n;
+        tile_range(count, g, k, &t0, &n);
+        const std::size_t nvec = (n + kE - 1) / kE;
+        if (!tile_fits(c, nvec * 16, kPipeBufBytes, 1, kPipeBufBytes)) return;
+        char* mine = c.stage[c.rank] + pipe_buf_offset(k);
+        const T* s = src + t0;
+        const bool s_al = aligned16(s);
+        batched_copy(nvec, [&](std::size_t v) { return load_guarded(s, v * kE, n, s_al); },
+                     [&](std::size_t v, const Vec16& x) { st_vec(mine + v * 16, x); });
+    };
+    auto stage_b = [&](int k) {
+        std::size_t t0, n;
+        tile_range(count, g, k, &t0, &n);
+        const std::size_t nvec = (n + kE - 1) / kE;
+        if (!tile_fits(c, nvec * 16, kPipeBufBytes, 1, kPipeBufBytes)) return;
+        const std::size_t off = pipe_buf_offset(k);
+        T* d = dst + t0;
+        const bool d_al = aligned16(d);
+        const std::size_t b = split_begin(n, N, c.rank, kE), e = split_begin(n, N, c.rank + 1, kE);
+        const std::size_t vb = (b + kE - 1) / kE, ve = (e + kE - 1) / kE;  // b == n when the slice is empty
+        batched_copy(ve - vb, [&](std::size_t v) { return multimem_ld_reduce_add<T>(c.stage_mc + off + (vb + v) * 16); },
+                     [&](std::size_t v, Vec16 x) {
+                         if constexpr (Op == RedOp::Avg) {
+                             Acc<T> a = unpack<T>(x);
+                             finish<Op, T>(a, inv);
+                             x = pack<T>(a);
+                         }
+                         multimem_st(c.stage_mc + off + (vb + v) * 16, x);
+                         store_guarded(d, (vb + v) * kE, n, d_al, x);
+                     });
+    };
+    auto stage_c = [&](int k) {
+        std::size_t t0, n;
+        tile_range(count, g, k, &t0, &n);
+        const std::size_t nvec = (n + kE - 1) / kE;
+        const char* mine = c.stage[c.rank] + pipe_buf_offset(k);
+        T* d = dst + t0;
+        const bool d_al = aligned16(d);
+        const std::size_t b = split_begin(n, N, c.rank, kE), e = split_begin(n, N, c.rank + 1, kE);
+        const std::size_t vb = (b + kE - 1) / kE, ve = (e + kE - 1) / kE;
+        // everything but my own slice: [0, vb) and [ve, nvec)
+        const std::size_t rest = nvec - (ve - vb);
+        batched_copy(rest, [&](std::size_t v) { return ld_vec_volatile(mine + (v < vb ? v : v + (ve - vb)) * 16); },
+                     [&](std::size_t v, const Vec16& x) { store_guarded(d, (v < vb ? v : v + (ve - vb)) * kE, n, d_al, x); });
+    };
+    pipe_run<true>(c, g.iters, stage_a, stage_b, stage_c);
+}
+
+// ------------------------------------------------------------------------------------------------
+// ReduceScatter, pipelined (two stages).  `count` = recv_count; g.slot_bytes = bytes of a tile.
+template <typename T, RedOp Op>
+__device__ __forceinline__ void
+rs_pipe_body(const CommDev& c, const T* src, T* dst, std::size_t count, const Geometry g) {
+    constexpr int kE = ElemsPerVec<T>::value;
+    const float inv = 1.0f / static_cast<float>(c.nranks);
+    const int N = c.nranks;
+    auto stage_a = [&](int k) {
+        std::size_t t0, n;
+        tile_range(count, g, k, &t0, &n);
+        const std::size_t nvec = (n + kE - 1) / kE;
+        if (!tile_fits(c, nvec * 16, g.slot_bytes, N, kPipeBufBytes)) return;
+        const std::size_t off = pipe_buf_offset(k);
+        for (int i = 1; i < N; ++i) {
+            const int j = (c.rank + i) % N;
+            const T* s = src + static_cast<std::size_t>(j) * count + t0;
+            const bool s_al = aligned16(s);
+            char* out = c.stage[j] + off + c.rank * g.slot_bytes;
+            batched_copy(nvec, [&](std::size_t v) { return load_guarded(s, v * kE, n, s_al); },
+                         [&](std::size_t v, const Vec16& x) { st_vec(out + v * 16, x); });
+        }
+    };
+    auto stage_b = [&](int k) {
+        std::size_t t0, n;
+        tile_range(count, g, k, &t0, &n);
+        const std::size_t nvec = (n + kE - 1) / kE;
+        if (!tile_fits(c, nvec * 16, g.slot_bytes, N, kPipeBufBytes)) return;
+        const T* own = src + static_cast<std::size_t>(c.rank) * count + t0;
+        const bool own_al = aligned16(own);
+        T* d = dst + t0;
+        const bool d_al = aligned16(d);
+        const char* in = c.stage[c.rank] + pipe_buf_offset(k);
+        for (std::size_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+            Acc<T> acc;
+            for (int r = 0; r < N; ++r) {
+                const Vec16 x = (r == c.rank) ? load_guarded(own, v * kE, n, own_al)
+                                              : ld_vec_volatile(in + r * g.slot_bytes + v * 16);
+                if (r == 0) acc = unpack<T>(x); else combine<Op, T>(acc, unpack<T>(x));
+            }
+            finish<Op, T>(acc, inv);
+            store_guarded(d, v * kE, n, d_al, pack<T>(acc));
+        }
+    };
+    pipe_run<false>(c, g.iters, stage_a, stage_b, [](int) {});
+}
+
+// ------------------------------------------------------------------------------------------------
+// AllGather, pipelined (two stages).  `count` = send_count; g.slot_bytes = bytes of a tile.
+template <typename T, bool kMc>
+__device__ __forceinline__ void
+ag_pipe_body(const CommDev& c, const T* src, T* dst, std::size_t count, const Geometry g) {
+    constexpr int kE = ElemsPerVec<T>::value;
+    const int N = c.nranks;
+    auto stage_a = [&](int k) {
+        std::size_t t0, n;
+        tile_range(count, g, k, &t0, &n);
+        const std::size_t nvec = (n + kE - 1) / kE;
+        if (!tile_fits(c, nvec * 16, g.slot_bytes, N, kPipeBufBytes)) return;
+        const std::size_t off = pipe_buf_offset(k) + c.rank * g.slot_bytes;
+        const T* s = src + t0;
+        const bool s_al = aligned16(s);
+        T* own = dst + static_cast<std::size_t>(c.rank) * count + t0;
+        const bool own_al = aligned16(own);
+        batched_copy(nvec, [&](std::size_t v) { return load_guarded(s, v * kE, n, s_al); },
+                     [&](std::size_t v, const Vec16& x) {
+                         store_guarded(own, v * kE, n, own_al, x);
+                         if constexpr (kMc) {
+                             multimem_st(c.stage_mc + off + v * 16, x);
+                         } else {
+                             for (int i = 1; i < N; ++i) st_vec(c.stage[(c.rank + i) % N] + off + v * 16, x);
+                         }
+                     });
+    };
+    auto stage_b = [&](int k) {
+        std::size_t t0, n;
+        tile_range(count, g, k, &t0, &n);
+        const std::size_t nvec = (n + kE - 1) / kE;
+        if (!tile_fits(c, nvec * 16, g.slot_bytes, N, kPipeBufBytes)) return;
+        const std::size_t off = pipe_buf_offset(k);
+        for (int i = 1; i < N; ++i) {
+            const int j = (c.rank + i) % N;
+            T* d = dst + static_cast<std::size_t>(j) * count + t0;
+            const bool d_al = aligned16(d);
+            const char* in = c.stage[c.rank] + off + j * g.slot_bytes;
+            batched_copy(nvec, [&](std::size_t v) { return ld_vec_volatile(in + v * 16); },
+                         [&](std::size_t v, const Vec16& x) { store_guarded(d, v * kE, n, d_al, x); });
+        }
+    };
+    pipe_run<false>(c, g.iters, stage_a, stage_b, [](int) {});
+}
+
+// ------------------------------------------------------------------------------------------------
+template <typename T, RedOp Op, bool kMc>
+NANO_KERNEL ar_twoshot_pipe_kernel(CommDev c, const T* src, T* dst, std::size_t count, const Geometry g) {
+    ar_twoshot_pipe_body<T, Op, kMc>(c, src, dst, count, g);
+}
+template <typename T, RedOp Op>
+NANO_KERNEL ar_twoshot_pipe_emu_kernel(const EmuRanks* e, std::size_t count, const Geometry g) {
+    const int r = blockIdx.y;
+    ar_twoshot_pipe_body<T, Op, false>(e->ctx[r], static_cast<const T*>(e->src[r]), static_cast<T*>(e->dst[r]), count, g);
+}
+template <typename T, RedOp Op>
+NANO_KERNEL ar_nvls_pipe_kernel(CommDev c, const T* src, T* dst, std::size_t count, const Geometry g) {
+    ar_nvls_pipe_body<T, Op>(c, src, dst, count, g);
+}
+template <typename T, RedOp Op>
+NANO_KERNEL rs_pipe_kernel(CommDev c, const T* src, T* dst, std::size_t count, const Geometry g) {
+    rs_pipe_body<T, Op>(c, src, dst, count, g);
+}
+template <typename T, RedOp Op>
+NANO_KERNEL rs_pipe_emu_kernel(const EmuRanks* e, std::size_t count, const Geometry g) {
+    const int r = blockIdx.y;
+    rs_pipe_body<T, Op>(e->ctx[r], static_cast<const T*>(e->src[r]), static_cast<T*>(e->dst[r]), count, g);
+}
+template <typename T, bool kMc>
+NANO_KERNEL ag_pipe_kernel(CommDev c, const T* src, T* dst, std::size_t count, const Geometry g) {
+    ag_pipe_body<T, kMc>(c, src, dst, count, g);
+}
+template <typename T>
+NANO_KERNEL ag_pipe_emu_kernel(const EmuRanks* e, std::size_t count, const Geometry g) {
+    const int r = blockIdx.y;
+    ag_pipe_body<T, false>(e->ctx[r], static_cast<const T*>(e->src[r]), static_cast<T*>(e->dst[r]), count, g);
+}
+
+}  // namespace nano_nccl::dev

@@ -10,7 +10,7 @@ pytestmark = pytest.mark.gpu
 WORKER = Path(__file__).resolve().parent / "workers" / "variant_checks.py"
 
 
-@pytest.mark.parametrize("case", ["bulk_copy", "emu_tma_allgather", "emu_ll", "fused_single"])
+@pytest.mark.parametrize("case", ["bulk_copy", "emu_tma_allgather", "emu_ll", "fused_single", "emu_pipe"])
 def test_variant(case):
     p = subprocess.run([sys.executable, str(WORKER), case], capture_output=True, text=True, timeout=600)
     assert p.returncode == 0 and f"{case} ok" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]

@@ -5,6 +5,8 @@
     emu_tma_allgather  AllGather whose pushes are TMA bulk copies (NANO_NCCL_PUSH_TMA=1), 2 / 4 / 8 emulated ranks
     emu_ll             flag-in-data small-message kernels (NANO_NCCL_LL_MAX_BYTES), 2 / 4 / 8 emulated ranks
     fused_single       plain GEMM and the fused GEMM kernels with one rank and every tile width
+    emu_pipe           software-pipelined large-message kernels (AllReduce two-shot, ReduceScatter, AllGather) with
+                       small tiles so that a CTA walks many of them, interleaved with the plain kernels
 
 Each check compares against a plain PyTorch result, uses guard bands, and relies on the kernels' bounded waits.
 tests/test_gpu_variants.py runs them.
@@ -146,6 +148,85 @@ def emu_ll():
     print("emu_ll ok")
 
 
+def emu_pipe():
+    """Pipelined kernels on emulated ranks: messages of 64 KiB and more take them (4 KiB tiles, so every CTA walks
+    many tiles and every buffer is reused several times); smaller messages in between take the plain kernels on
+    the same staging memory, which exercises the barriers at both ends of a pipelined kernel."""
+    os.environ["NANO_NCCL_PIPE_MIN_BYTES"] = str(64 * 1024)
+    os.environ["NANO_NCCL_PIPE_TILE_BYTES"] = "4096"
+    lib = N.load_library()
+    stream = torch.cuda.current_stream().cuda_stream
+    tol = {torch.float32: 1e-5, torch.float16: 2e-3, torch.bfloat16: 1.6e-2}
+    code = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+    def ref(xs, op):
+        acc = torch.stack([x.float() for x in xs])
+        return {"sum": acc.sum(0), "avg": acc.sum(0) / len(xs), "max": acc.max(0).values, "min": acc.min(0).values}[op]
+
+    def guarded(n, dtype):
+        full = torch.full((n + 2 * GUARD,), float(SENTINEL), dtype=dtype, device="cuda")
+        return full, full[GUARD:GUARD + n]
+
+    def clean(h, nranks):
+        words = (C.c_uint32 * 4)()
+        for r in range(nranks):
+            N.check(lib.nano_nccl_emu_status(h, r, words))
+            assert words[0] == 0, ("device status", r, list(words))
+
+    for nranks in (2, 3, 4, 8):
+        h = C.c_void_p()
+        N.check(lib.nano_nccl_emu_create(0, nranks, 5_000_000, C.byref(h)))
+        try:
+            for dtype in (torch.float32, torch.bfloat16, torch.float16):
+                esz = torch.empty((), dtype=dtype).element_size()
+                # below the threshold (plain), just above, odd and unaligned, several tiles per CTA, a large one
+                for count in (1000, 64 * 1024 // esz, 70001, 300_003, 1_500_000):
+                    for op in (("sum", "max") if count > 100000 else ("sum", "avg", "max", "min")):
+                        xs = [(torch.rand(count, device="cuda") * 2 - 1).to(dtype) for _ in range(nranks)]
+                        outs = [guarded(count, dtype) for _ in range(nranks)]
+                        src = (C.c_void_p * nranks)(*[x.data_ptr() for x in xs])
+                        dst = (C.c_void_p * nranks)(*[o[1].data_ptr() for o in outs])
+                        N.check(lib.nano_nccl_emu_all_reduce(h, src, dst, count, code[dtype], N.REDOPS[op],
+                                                             N.ALGOS["twoshot"], 12, stream))
+                        torch.cuda.synchronize()
+                        clean(h, nranks)
+                        want = ref(xs, op).to(dtype).float()
+                        for full, out in outs:
+                            assert ((out.float() - want).abs() <= tol[dtype] * want.abs().clamp(min=1)).all(), ("ar", nranks, dtype, count, op)
+                            assert (full[:GUARD] == SENTINEL).all() and (full[-GUARD:] == SENTINEL).all()
+                        assert all(torch.equal(outs[0][1], o[1]) for o in outs), "ranks disagree bit-wise"
+                    per = max(1, count // nranks)
+                    for op in ("sum", "min"):
+                        xs = [(torch.rand(per * nranks, device="cuda") * 2 - 1).to(dtype) for _ in range(nranks)]
+                        outs = [guarded(per, dtype) for _ in range(nranks)]
+                        src = (C.c_void_p * nranks)(*[x.data_ptr() for x in xs])
+                        dst = (C.c_void_p * nranks)(*[o[1].data_ptr() for o in outs])
+                        N.check(lib.nano_nccl_emu_reduce_scatter(h, src, dst, per, code[dtype], N.REDOPS[op], 12, stream))
+                        torch.cuda.synchronize()
+                        clean(h, nranks)
+                        want = ref(xs, op).to(dtype).float()
+                        for r, (full, out) in enumerate(outs):
+                            w = want[r * per:(r + 1) * per]
+                            assert ((out.float() - w).abs() <= tol[dtype] * w.abs().clamp(min=1)).all(), ("rs", nranks, dtype, per, op)
+                            assert (full[:GUARD] == SENTINEL).all() and (full[-GUARD:] == SENTINEL).all()
+                    if dtype != torch.float16:
+                        xs = [(torch.rand(per, device="cuda") * 2 - 1).to(dtype) for _ in range(nranks)]
+                        outs = [guarded(per * nranks, dtype) for _ in range(nranks)]
+                        src = (C.c_void_p * nranks)(*[x.data_ptr() for x in xs])
+                        dst = (C.c_void_p * nranks)(*[o[1].data_ptr() for o in outs])
+                        N.check(lib.nano_nccl_emu_all_gather(h, src, dst, per, code[dtype], 12, stream))
+                        torch.cuda.synchronize()
+                        clean(h, nranks)
+                        want = torch.cat(xs)
+                        for full, out in outs:
+                            assert torch.equal(out, want), ("ag", nranks, dtype, per)
+                            assert (full[:GUARD] == SENTINEL).all() and (full[-GUARD:] == SENTINEL).all()
+        finally:
+            lib.nano_nccl_emu_destroy(h)
+    del os.environ["NANO_NCCL_PIPE_MIN_BYTES"], os.environ["NANO_NCCL_PIPE_TILE_BYTES"]
+    print("emu_pipe ok")
+
+
 def fused_single():
     """The fused GEMM kernels with ONE rank (all tiles are own tiles, nothing crosses NVLink) and the plain GEMM,
     with the run-time tile widths, against fp32 products."""
@@ -184,3 +265,5 @@ if __name__ == "__main__":
         emu_ll()
     if which in ("fused_single", "all"):
         fused_single()
+    if which in ("emu_pipe", "all"):
+        emu_pipe()
