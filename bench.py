@@ -243,7 +243,7 @@ def main() -> None:
     dev_ms = reduce_max(dev_ms)
     e2e_ms = reduce_max(e2e_ms)
     breakdown = None
-    if args.impl == "nano" and world > 1:   # three more steps with events around every bucket's reduction (not timed above)
+    if args.impl == "nano":   # three more steps with events around every bucket's reduction (not timed above)
         engine.enable_timeline(True)
         for i in range(3):
             train_step(dev_idx[i % pool], dev_tgt[i % pool])

@@ -4,6 +4,10 @@
     python -m nano_nccl_b200.bench.profile_cases emu_twoshot # 8 emulated ranks, 32 MiB bf16 two-shot AllReduce
     python -m nano_nccl_b200.bench.profile_cases adamw       # fused AdamW over 64 Mi parameters
     python -m nano_nccl_b200.bench.profile_cases emu_oneshot | emu_reduce_scatter | emu_all_gather   # 8 emulated ranks, 32 MiB
+    python -m nano_nccl_b200.bench.profile_cases emu_ll      # 8 emulated ranks, 256 KiB flag-in-data AllReduce
+    python -m nano_nccl_b200.bench.profile_cases gemm_rs_single | ag_gemm_single   # fused GEMM kernels, one rank, 8192 x 4096 x 1792
+
+Messages of 8 MiB and more take the software-pipelined kernels (NANO_NCCL_PIPE_MIN_BYTES=0 selects the plain ones).
 
 Each case also prints its CUDA-event time so the capture can be compared with an unprofiled run.
 """
@@ -90,6 +94,45 @@ def _emu(kind: str):
     lib.nano_nccl_emu_destroy(h)
 
 
+def emu_ll():
+    """Flag-in-data one-shot AllReduce of 256 KiB on 8 emulated ranks (the small-message kernel)."""
+    import os
+
+    os.environ["NANO_NCCL_LL_MAX_BYTES"] = str(1 << 20)
+    lib = N.load_library()
+    nranks, count = 8, 128 * 1024  # 256 KiB of bf16 per rank
+    h = C.c_void_p()
+    N.check(lib.nano_nccl_emu_create(0, nranks, 5_000_000, C.byref(h)))
+    xs = [torch.randn(count, device="cuda").bfloat16() for _ in range(nranks)]
+    outs = [torch.empty_like(x) for x in xs]
+    src = (C.c_void_p * nranks)(*[x.data_ptr() for x in xs])
+    dst = (C.c_void_p * nranks)(*[o.data_ptr() for o in outs])
+    stream = torch.cuda.current_stream().cuda_stream
+    us = _time(lambda: N.check(lib.nano_nccl_emu_all_reduce(h, src, dst, count, 2, N.REDOPS["sum"], N.ALGOS["oneshot"], 16, stream)), reps=5)
+    print(f"emulated flag-in-data all_reduce, {nranks} ranks x {count * 2 >> 10} KiB: {us:.1f} us")
+    lib.nano_nccl_emu_destroy(h)
+
+
+def _fused_single(which: str):
+    """The fused GEMM kernels with one rank: every tile is an own tile, nothing crosses NVLink, so a capture shows
+    the tensor pipe and the epilogue of the fused modes without peers."""
+    from nano_nccl_b200 import Communicator
+    from nano_nccl_b200.ops.gemm import FusedTensorParallel, gemm_last_error
+
+    comm = Communicator.from_tcp("127.0.0.1", 29631, 0, 1, device=0)
+    m, n, k = (8192, 4096, 1792) if which == "gemm_rs" else (8192, 1792, 4096)
+    fused = FusedTensorParallel(comm, m * n * 2, m * k * 2)
+    a = torch.randn(m, k, device="cuda").bfloat16()
+    w = (torch.randn(n, k, device="cuda") * 0.02).bfloat16()
+    out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    fn = (lambda: fused.gemm_rs(a, w, out=out)) if which == "gemm_rs" else (lambda: fused.ag_gemm(a, w, out=out))
+    us = _time(fn)
+    assert gemm_last_error() == 0
+    print(f"{which} single rank {m}x{n}x{k}: {us:.1f} us, {2.0 * m * n * k / us / 1e6:.0f} TFLOP/s")
+    fused.destroy()
+    comm.destroy()
+
+
 def adamw():
     from nano_nccl_b200.ops.optim import adamw_step_
 
@@ -104,4 +147,5 @@ def adamw():
 
 if __name__ == "__main__":
     {"gemm": gemm, "emu_twoshot": emu_twoshot, "adamw": adamw, "emu_oneshot": lambda: _emu("oneshot"),
-     "emu_reduce_scatter": lambda: _emu("reduce_scatter"), "emu_all_gather": lambda: _emu("all_gather")}[sys.argv[1]]()
+     "emu_reduce_scatter": lambda: _emu("reduce_scatter"), "emu_all_gather": lambda: _emu("all_gather"), "emu_ll": emu_ll,
+     "gemm_rs_single": lambda: _fused_single("gemm_rs"), "ag_gemm_single": lambda: _fused_single("ag_gemm")}[sys.argv[1]]()

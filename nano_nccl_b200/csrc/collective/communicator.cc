@@ -47,6 +47,11 @@ const char* phase_name(std::uint32_t phase) {
     }
 }
 
+// Largest message of the flag-in-data kernels when the environment does not say.  Two ranks: measured 12.3-12.8 us
+// against 14.5-16.3 us at 256 KiB and level at 1 MiB (p50, device-timed); the data crosses one pair of links, so
+// the doubled bytes cost little.  More ranks: kept off until a sweep on that many GPUs has shown a gain.
+std::int64_t default_ll_max_bytes(int nranks) { return nranks == 2 ? (1 << 20) : 0; }
+
 }  // namespace
 
 // ------------------------------------------------------------------------------------------------
@@ -156,8 +161,11 @@ Communicator::Impl::Impl(std::shared_ptr<Bootstrap> bootstrap, const Communicato
         arena_ = SymmetricMemory::create(*bootstrap_, fds_.get(), device_, dev::kArenaBytes, options);
         state_ = RawDeviceBuffer(device_, sizeof(dev::BlockState) * dev::kMaxBlocks, true);
         fill_device_context();
-        // Flag-in-data kernels for small messages (NANO_NCCL_LL_MAX_BYTES > 0): a staging segment of their own.
-        ll_max_bytes_ = static_cast<std::size_t>(env::integer("NANO_NCCL_LL_MAX_BYTES", 0, 0, 16 << 20));
+        // Flag-in-data kernels for small messages, in a staging segment of their own.  NANO_NCCL_LL_MAX_BYTES is the
+        // largest message that takes them (AllReduce message; ReduceScatter / AllGather: the whole N-chunk buffer),
+        // 0 switches them off.  Default: kDefaultLLMaxBytes where they were measured faster than the barrier
+        // kernels (see default_ll_max_bytes).
+        ll_max_bytes_ = static_cast<std::size_t>(env::integer("NANO_NCCL_LL_MAX_BYTES", default_ll_max_bytes(nranks_), 0, 16 << 20));
         if (nranks_ > 1) {
             NANO_REQUIRE_ARG(bootstrap_->all_reduce_min(static_cast<std::int64_t>(ll_max_bytes_)) ==
                                  bootstrap_->all_reduce_max(static_cast<std::int64_t>(ll_max_bytes_)),

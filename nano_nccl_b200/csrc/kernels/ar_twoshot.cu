@@ -1,5 +1,7 @@
 #include "kernels/dispatch.cuh"
 
+#include <type_traits>
+
 namespace nano_nccl::dev {
 
 cudaError_t launch_ar_twoshot(const CommDev& c, const void* src, void* dst, std::size_t count,
@@ -35,10 +37,19 @@ cudaError_t launch_ar_symm_p2p(const CommDev& c, const void* const* src_peers, v
         using T = decltype(t);
         return dispatch_op(op, [&](auto o) {
             constexpr RedOp Op = decltype(o)::value;
-            if (one_shot) {
-                ar_symm_p2p_kernel<T, Op, true><<<grid, kCollectiveThreads, 0, stream>>>(c, p, nvec);
-            } else {
-                ar_symm_p2p_kernel<T, Op, false><<<grid, kCollectiveThreads, 0, stream>>>(c, p, nvec);
+            auto launch = [&](auto n_tag) {
+                constexpr int kN = decltype(n_tag)::value;
+                if (one_shot) {
+                    ar_symm_p2p_kernel<T, Op, true, kN><<<grid, kCollectiveThreads, 0, stream>>>(c, p, nvec);
+                } else {
+                    ar_symm_p2p_kernel<T, Op, false, kN><<<grid, kCollectiveThreads, 0, stream>>>(c, p, nvec);
+                }
+            };
+            switch (c.nranks) {  // the common rank counts get loops unrolled over the ranks with several vectors in flight
+                case 2: launch(std::integral_constant<int, 2>{}); break;
+                case 4: launch(std::integral_constant<int, 4>{}); break;
+                case 8: launch(std::integral_constant<int, 8>{}); break;
+                default: launch(std::integral_constant<int, 0>{}); break;
             }
             return cudaGetLastError();
         });

@@ -575,13 +575,19 @@ struct SymmPeers {
     char* dst[kMaxRanks];
 };
 
-template <typename T, RedOp Op, bool kOneShot>
+// kN: the rank count as a compile-time constant (2, 4, 8), or 0 for "whatever c.nranks says".  With kN known a
+// thread keeps 16 / kN vectors of every rank in flight (16 loads of 16 bytes); a single vector per thread, as in the
+// generic form, leaves a CTA at a few GB/s over NVLink, which matters when only a few CTAs may be spared for the
+// reduction (gradient buckets beside a backward pass).
+template <typename T, RedOp Op, bool kOneShot, int kN>
 __device__ __forceinline__ void
 ar_symm_p2p_body(const CommDev& c, const SymmPeers& p, std::size_t nvec_total) {
     std::uint32_t epoch = c.state[blockIdx.x].epoch;
     const std::uint32_t seq = c.state[blockIdx.x].seq;
     const float inv = 1.0f / static_cast<float>(c.nranks);
-    const int N = c.nranks;
+    const int N = kN != 0 ? kN : c.nranks;
+    constexpr int kVecs = kN != 0 ? 16 / kN : 1;   // vectors per thread and pass
+    constexpr int kR = kN != 0 ? kN : kMaxRanks;   // unrolled rank loop bound
     if (block_barrier(c, epoch, 1)) {  // every rank's input is complete
         std::size_t vb = 0, ve = nvec_total;
         if (!kOneShot) {
@@ -590,25 +596,34 @@ ar_symm_p2p_body(const CommDev& c, const SymmPeers& p, std::size_t nvec_total) {
             ve = vb + per < nvec_total ? vb + per : nvec_total;
         }
         const std::size_t stride = static_cast<std::size_t>(gridDim.x) * blockDim.x;
-        for (std::size_t v = vb + blockIdx.x * blockDim.x + threadIdx.x; v < ve; v += stride) {
-            Vec16 x[kMaxRanks];
+        for (std::size_t v0 = vb + blockIdx.x * blockDim.x + threadIdx.x; v0 < ve; v0 += kVecs * stride) {
+            Vec16 x[kVecs][kR];
 #pragma unroll
-            for (int r = 0; r < kMaxRanks; ++r) {
-                if (r < N) x[r] = ld_vec_volatile(p.src[r] + v * 16);  // all loads in flight together
+            for (int k = 0; k < kVecs; ++k) {
+                const std::size_t v = v0 + k * stride;
+#pragma unroll
+                for (int r = 0; r < kR; ++r) {
+                    if (r < N && v < ve) x[k][r] = ld_vec_volatile(p.src[r] + v * 16);  // all loads in flight together
+                }
             }
-            Acc<T> acc = unpack<T>(x[0]);
 #pragma unroll
-            for (int r = 1; r < kMaxRanks; ++r) {
-                if (r < N) combine<Op, T>(acc, unpack<T>(x[r]));
-            }
-            finish<Op, T>(acc, inv);
-            const Vec16 y = pack<T>(acc);
-            if (kOneShot) {
-                st_vec(p.dst[c.rank] + v * 16, y);
-            } else {
+            for (int k = 0; k < kVecs; ++k) {
+                const std::size_t v = v0 + k * stride;
+                if (v >= ve) continue;
+                Acc<T> acc = unpack<T>(x[k][0]);
 #pragma unroll
-                for (int i = 0; i < kMaxRanks; ++i) {
-                    if (i < N) st_vec(p.dst[(c.rank + i) % N] + v * 16, y);
+                for (int r = 1; r < kR; ++r) {
+                    if (r < N) combine<Op, T>(acc, unpack<T>(x[k][r]));
+                }
+                finish<Op, T>(acc, inv);
+                const Vec16 y = pack<T>(acc);
+                if (kOneShot) {
+                    st_vec(p.dst[c.rank] + v * 16, y);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < kR; ++i) {
+                        if (i < N) st_vec(p.dst[(c.rank + i) % N] + v * 16, y);
+                    }
                 }
             }
         }
@@ -763,9 +778,9 @@ NANO_KERNEL ag_symm_kernel(CommDev c, const char* src, SymmPeers p, char* dst_mc
     ag_symm_body<kMc>(c, src, p, dst_mc, nvec_chunk);
 }
 
-template <typename T, RedOp Op, bool kOneShot>
+template <typename T, RedOp Op, bool kOneShot, int kN>
 NANO_KERNEL ar_symm_p2p_kernel(CommDev c, SymmPeers p, std::size_t nvec_total) {
-    ar_symm_p2p_body<T, Op, kOneShot>(c, p, nvec_total);
+    ar_symm_p2p_body<T, Op, kOneShot, kN>(c, p, nvec_total);
 }
 
 template <typename T, RedOp Op>

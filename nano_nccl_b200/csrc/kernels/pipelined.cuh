@@ -17,7 +17,8 @@
 // signals after its C(k).  Two-stage kernels (ReduceScatter, AllGather) wait for B(k-3) before A(k).
 //
 // Signals are two monotonic counters per (CTA, peer): stream A in the ordinary pad row (the same words and
-// the same epoch counter as block_barrier, of which a signal is one half), stream B in a second row.
+// the same epoch counter as block_barrier, of which a signal is one half), stream B in a second row.  They
+// are issued by a warp of their own, so that the data warps never sit in a release fence (see PipeShared).
 // A kernel starts and ends with a full barrier, because the plain kernels index the same staging bytes by
 // halves: the first keeps the pushes away from a peer that is still copying out of the previous kernel's
 // half, the last lets the next kernel write anywhere.  All waits are bounded like everywhere else.
@@ -41,61 +42,133 @@ __device__ __forceinline__ std::size_t pipe_buf_offset(int k) {
     return static_cast<std::size_t>(blockIdx.x) * kBlockStageBytes + static_cast<std::size_t>(k % kPipeDepth) * kPipeBufBytes;
 }
 
-// Threads 0..N-1 store `value` into the flag word (row, this block, this rank) of their peer.  The caller has
-// just passed a __syncthreads, so the release covers everything the block wrote before it.
-__device__ __forceinline__ void pipe_signal(const CommDev& c, std::size_t row, std::uint32_t value) {
-    const int peer = static_cast<int>(threadIdx.x);
-    if (peer < c.nranks && peer != c.rank) {
-        st_release_sys(c.pad[peer] + row + blockIdx.x * kPadWordsPerBlock + c.rank, value);
+// Roles inside a CTA: warps 0..14 (kPipeDataThreads) move data; warp 15 only signals.  A signal is a release
+// store at system scope, i.e. a fence that waits until the CTA's earlier remote stores have been acknowledged
+// over NVLink, which on a saturated link takes as long as draining everything queued before them.  If the data
+// warps issued it themselves, every stage would end with that drain and nothing would overlap (measured: the
+// pipeline was slower than the plain kernels).  So a data thread only arrives on a shared-memory mbarrier when
+// a stage is done (release at CTA scope) and moves on; the signalling warp acquires the mbarrier phase, runs
+// the fence and stores the flags.  The two release steps chain (CTA scope, then system scope), so a peer that
+// acquires the flag sees the stage's data.
+constexpr int kPipeDataThreads = kCollectiveThreads - 32;
+
+struct PipeShared {
+    std::uint64_t bar_a;                 // data threads arrive when stage A of a tile is issued
+    std::uint64_t bar_b;                 // ... when stage B of a tile is done
+    volatile std::uint32_t taken_a;      // phases of bar_a the signalling warp has consumed
+    volatile std::uint32_t taken_b;
+    volatile std::uint32_t failed;       // a bounded wait ran out somewhere in the CTA
+    std::uint32_t giveup;                // wait_flag's cross-thread cancel word
+    volatile std::uint32_t verdict;      // `failed` as thread 0 read it between two barriers: the same for every data thread
+};
+
+__device__ __forceinline__ void pipe_data_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kPipeDataThreads) : "memory"); }
+
+// A data thread reports "stage done" for phase `index` of `bar`.  It first makes sure the signalling warp has
+// consumed every earlier phase (an mbarrier tracks one pending phase), which it normally has long ago.
+__device__ __forceinline__ void pipe_hand_over(const CommDev& c, PipeShared& sh, std::uint64_t* bar,
+                                               volatile std::uint32_t* taken, std::uint32_t index) {
+    if (*taken < index) {
+        const unsigned long long start = global_timer_ns();
+        while (*taken < index && sh.failed == 0u) {
+            if (global_timer_ns() - start > c.timeout_ns) sh.failed = 1u;
+        }
     }
+    gemm::mbar_arrive(bar);
 }
 
-// Waits until every peer's flag word (row, this block) has reached `target`; uniform result over the block.
-__device__ __forceinline__ bool pipe_wait(const CommDev& c, std::size_t row, std::uint32_t target, int phase,
-                                          volatile std::uint32_t* giveup) {
-    int ok = 1;
+// Data threads: wait until every peer's flag word (row, this block) has reached `target`; uniform over the data warps.
+__device__ __forceinline__ bool pipe_wait(const CommDev& c, PipeShared& sh, std::size_t row, std::uint32_t target, int phase) {
     const int peer = static_cast<int>(threadIdx.x);
     if (peer < c.nranks && peer != c.rank) {
-        ok = wait_flag(c, c.pad[c.rank] + row + blockIdx.x * kPadWordsPerBlock + peer, target, peer, phase, giveup,
-                       peer == (c.rank == 0 ? 1 : 0)) ? 1 : 0;
+        if (!wait_flag(c, c.pad[c.rank] + row + blockIdx.x * kPadWordsPerBlock + peer, target, peer, phase, &sh.giveup,
+                       peer == (c.rank == 0 ? 1 : 0))) {
+            sh.failed = 1u;
+        }
     }
-    return __syncthreads_and(ok) != 0;
+    // `failed` may be raised by the signalling warp at any moment, so the data warps must not each read it: one
+    // thread reads it, and everybody uses that reading (a split decision would leave threads at different barriers).
+    pipe_data_sync();
+    if (threadIdx.x == 0) sh.verdict = sh.failed;
+    pipe_data_sync();
+    return sh.verdict == 0u;
 }
 
-// The schedule.  stage_a / stage_b / stage_c take the tile index; kThree selects the three-stage form.
+// Signalling warp: acquire phase `index` of `bar` (bounded), then store `value` into the peers' flag words.
+__device__ __forceinline__ bool pipe_signal_when_done(const CommDev& c, PipeShared& sh, std::uint64_t* bar,
+                                                      volatile std::uint32_t* taken, std::uint32_t index, std::size_t row,
+                                                      std::uint32_t value) {
+    const unsigned long long start = global_timer_ns();
+    unsigned spins = 0;
+    while (!gemm::mbar_try_wait(bar, index & 1u)) {
+        if ((++spins & 63u) == 0u) {
+            if (sh.failed != 0u) return false;
+            if (global_timer_ns() - start > 2 * c.timeout_ns) {
+                sh.failed = 1u;
+                return false;
+            }
+        }
+    }
+    const int lane = static_cast<int>(threadIdx.x) - kPipeDataThreads;
+    if (lane == 0) *taken = index + 1u;
+    if (lane < c.nranks && lane != c.rank) {
+        st_release_sys(c.pad[lane] + row + blockIdx.x * kPadWordsPerBlock + c.rank, value);
+    }
+    return true;
+}
+
+// The schedule.  stage_a / stage_b / stage_c take the tile index and are run by the data threads (they must
+// stride by kPipeDataThreads); kThree selects the three-stage form.
 template <bool kThree, typename FA, typename FB, typename FC>
 __device__ __forceinline__ void pipe_run(const CommDev& c, int tiles, FA&& stage_a, FB&& stage_b, FC&& stage_c) {
-    __shared__ std::uint32_t giveup;
+    __shared__ PipeShared sh;
     std::uint32_t epoch = c.state[blockIdx.x].epoch;
     std::uint32_t epoch_b = c.state[blockIdx.x].epoch_b;
     const std::uint32_t seq = c.state[blockIdx.x].seq;
-    if (threadIdx.x == 0) giveup = 0u;
-    bool ok = block_barrier(c, epoch, 1);
+    if (threadIdx.x == 0) {
+        gemm::mbar_init(&sh.bar_a, kPipeDataThreads);
+        gemm::mbar_init(&sh.bar_b, kPipeDataThreads);
+        sh.taken_a = 0u;
+        sh.taken_b = 0u;
+        sh.failed = 0u;
+        sh.giveup = 0u;
+        sh.verdict = 0u;
+        gemm::fence_barrier_init();
+    }
+    bool ok = block_barrier(c, epoch, 1);  // also publishes the shared-memory set-up to every warp
     const std::uint32_t a0 = epoch, b0 = epoch_b;  // signal A(k) carries a0 + k + 1, signal B(k) carries b0 + k + 1
     const int last = tiles + (kThree ? 1 : 0);
-    for (int k = 0; ok && k <= last; ++k) {
-        if (k < tiles) {
-            if (!kThree && k >= kPipeDepth) {
-                ok = pipe_wait(c, kPipeFlagRowWords, b0 + static_cast<std::uint32_t>(k - kPipeDepth) + 1u, 3, &giveup);
-                if (!ok) break;
+    if (ok && threadIdx.x >= kPipeDataThreads) {
+        // ---- signalling warp: the data warps' hand-overs in their program order
+        for (int k = 0; k <= last; ++k) {
+            if (k < tiles && !pipe_signal_when_done(c, sh, &sh.bar_a, &sh.taken_a, static_cast<std::uint32_t>(k), 0,
+                                                    a0 + static_cast<std::uint32_t>(k) + 1u)) break;
+            if (k >= 1 && k - 1 < tiles &&
+                !pipe_signal_when_done(c, sh, &sh.bar_b, &sh.taken_b, static_cast<std::uint32_t>(k - 1), kPipeFlagRowWords,
+                                       b0 + static_cast<std::uint32_t>(k))) break;
+        }
+    } else if (ok) {
+        // ---- data warps
+        for (int k = 0; k <= last; ++k) {
+            if (k < tiles) {
+                if (!kThree && k >= kPipeDepth &&
+                    !pipe_wait(c, sh, kPipeFlagRowWords, b0 + static_cast<std::uint32_t>(k - kPipeDepth) + 1u, 3)) break;
+                stage_a(k);
+                pipe_hand_over(c, sh, &sh.bar_a, &sh.taken_a, static_cast<std::uint32_t>(k));
             }
-            stage_a(k);
-            __syncthreads();
-            pipe_signal(c, 0, a0 + static_cast<std::uint32_t>(k) + 1u);
-        }
-        if (kThree && k >= 2 && k - 2 < tiles) {
-            ok = pipe_wait(c, kPipeFlagRowWords, b0 + static_cast<std::uint32_t>(k - 2) + 1u, 4, &giveup);
-            if (!ok) break;
-            stage_c(k - 2);
-        }
-        if (k >= 1 && k - 1 < tiles) {
-            ok = pipe_wait(c, 0, a0 + static_cast<std::uint32_t>(k), 3, &giveup);
-            if (!ok) break;
-            stage_b(k - 1);
-            __syncthreads();
-            pipe_signal(c, kPipeFlagRowWords, b0 + static_cast<std::uint32_t>(k));
+            if (kThree && k >= 2 && k - 2 < tiles) {
+                if (!pipe_wait(c, sh, kPipeFlagRowWords, b0 + static_cast<std::uint32_t>(k - 2) + 1u, 4)) break;
+                stage_c(k - 2);
+            }
+            if (k >= 1 && k - 1 < tiles) {
+                if (!pipe_wait(c, sh, 0, a0 + static_cast<std::uint32_t>(k), 3)) break;
+                stage_b(k - 1);
+                pipe_hand_over(c, sh, &sh.bar_b, &sh.taken_b, static_cast<std::uint32_t>(k - 1));
+            }
         }
     }
+    __syncthreads();
+    ok = ok && sh.failed == 0u;
     if (ok) {
         epoch = a0 + static_cast<std::uint32_t>(tiles);
         epoch_b = b0 + static_cast<std::uint32_t>(tiles);
@@ -108,22 +181,22 @@ __device__ __forceinline__ void pipe_run(const CommDev& c, int tiles, FA&& stage
     }
 }
 
-// Copies `nvec` 16-byte vectors with kPipeBatch loads in flight per thread.  LoadFn(v) -> Vec16, StoreFn(v, x).
-// Four per thread (2048 per CTA, 32 KiB) cover the bandwidth-delay product of a CTA's share of NVLink several
+// Copies `nvec` 16-byte vectors with kPipeBatch loads in flight per data thread.  LoadFn(v) -> Vec16, StoreFn(v, x).
+// Four per thread (1920 per CTA, 30 KiB) cover the bandwidth-delay product of a CTA's share of NVLink several
 // times over and leave the three inlined stages enough registers under the 128-register cap of a 512-thread CTA.
 constexpr int kPipeBatch = 4;
 template <typename LoadFn, typename StoreFn>
 __device__ __forceinline__ void batched_copy(std::size_t nvec, LoadFn&& load, StoreFn&& store) {
-    for (std::size_t v0 = threadIdx.x; v0 < nvec; v0 += kPipeBatch * blockDim.x) {
+    for (std::size_t v0 = threadIdx.x; v0 < nvec; v0 += kPipeBatch * kPipeDataThreads) {
         Vec16 x[kPipeBatch];
 #pragma unroll
         for (int k = 0; k < kPipeBatch; ++k) {
-            const std::size_t v = v0 + k * blockDim.x;
+            const std::size_t v = v0 + k * kPipeDataThreads;
             if (v < nvec) x[k] = load(v);
         }
 #pragma unroll
         for (int k = 0; k < kPipeBatch; ++k) {
-            const std::size_t v = v0 + k * blockDim.x;
+            const std::size_t v = v0 + k * kPipeDataThreads;
             if (v < nvec) store(v, x[k]);
         }
     }
@@ -168,7 +241,7 @@ ar_twoshot_pipe_body(const CommDev& c, const T* src, T* dst, std::size_t count, 
         const std::size_t len = e - b, nvec = (len + kE - 1) / kE;
         const char* in = c.stage[c.rank] + off;
         const std::size_t go = off + kGatherOff + c.rank * g.slot_bytes;
-        for (std::size_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+        for (std::size_t v = threadIdx.x; v < nvec; v += kPipeDataThreads) {
             Acc<T> acc;
             for (int r = 0; r < N; ++r) {
                 const Vec16 x = (r == c.rank) ? load_guarded(s + b, v * kE, len, s_al)
@@ -295,7 +368,7 @@ rs_pipe_body(const CommDev& c, const T* src, T* dst, std::size_t count, const Ge
         T* d = dst + t0;
         const bool d_al = aligned16(d);
         const char* in = c.stage[c.rank] + pipe_buf_offset(k);
-        for (std::size_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+        for (std::size_t v = threadIdx.x; v < nvec; v += kPipeDataThreads) {
             Acc<T> acc;
             for (int r = 0; r < N; ++r) {
                 const Vec16 x = (r == c.rank) ? load_guarded(own, v * kE, n, own_al)

@@ -86,7 +86,7 @@ class DataParallel:
         self.shard = bool(shard_optimizer) and self.world > 1
         self.step_count = 0
         self.timeline = False
-        self._t_forward = self._t_backward_end = self._t_step_end = None
+        self._t_forward = self._t_forward_end = self._t_backward_end = self._t_step_end = None
         self.collective_launches = 0
         self.optimizer_launches = 0
         params = [p for p in module.parameters() if p.requires_grad]
@@ -159,7 +159,7 @@ class DataParallel:
         tail = self.tail_full_grid and self.comm_ctas > 0 and b is self.buckets[-1] and len(self.buckets) > 1
         if tail:
             self.comm.set_grid_override(0)   # the tuner's own grid for this size
-        if self.timeline:
+        if self.timeline and b.t_start is not None:
             b.t_start.record(self.comm_stream)
         if self.shard:
             self.comm.reduce_scatter(b.flat_grad, b.grad_shard, "avg", stream=self.comm_stream)
@@ -183,17 +183,20 @@ class DataParallel:
             b.launched = False
 
     def forward(self, *args, **kwargs):
-        if self.timeline:
-            self._t_forward.record()
-        return self.module(*args, **kwargs)
+        if not self.timeline:
+            return self.module(*args, **kwargs)
+        self._t_forward.record()
+        out = self.module(*args, **kwargs)
+        self._t_forward_end.record()
+        return out
 
     # ------------------------------------------------------------------ time line
     def enable_timeline(self, on: bool = True) -> None:
         """Records CUDA events around every bucket's reduction and around the step, for `timeline_summary`."""
-        self.timeline = bool(on) and self.world > 1
+        self.timeline = bool(on)
         if self.timeline and self._t_forward is None:
             mk = lambda: torch.cuda.Event(enable_timing=True)
-            self._t_forward, self._t_backward_end, self._t_step_end = mk(), mk(), mk()
+            self._t_forward, self._t_forward_end, self._t_backward_end, self._t_step_end = mk(), mk(), mk(), mk()
             for b in self.buckets:
                 b.t_start, b.t_done = mk(), mk()
 
@@ -207,12 +210,16 @@ class DataParallel:
             return None
         torch.cuda.synchronize()
         t0 = self._t_forward
-        rows = [{"bytes": b.numel * 2, "start_ms": round(t0.elapsed_time(b.t_start), 3),
-                 "end_ms": round(t0.elapsed_time(b.t_done), 3)} for b in self.buckets]
         bwd_end = t0.elapsed_time(self._t_backward_end)
         step_end = t0.elapsed_time(self._t_step_end)
+        fwd_end = round(t0.elapsed_time(self._t_forward_end), 3)
+        if self.world == 1:
+            return {"forward_end_ms": fwd_end, "backward_end_ms": round(bwd_end, 3), "step_end_ms": round(step_end, 3),
+                    "exposed_ms": round(step_end - bwd_end, 3)}
+        rows = [{"bytes": b.numel * 2, "start_ms": round(t0.elapsed_time(b.t_start), 3),
+                 "end_ms": round(t0.elapsed_time(b.t_done), 3)} for b in self.buckets]
         last_done = max(r["end_ms"] for r in rows)
-        return {"backward_end_ms": round(bwd_end, 3), "step_end_ms": round(step_end, 3),
+        return {"forward_end_ms": fwd_end, "backward_end_ms": round(bwd_end, 3), "step_end_ms": round(step_end, 3),
                 "exposed_ms": round(step_end - bwd_end, 3), "last_reduction_end_ms": round(last_done, 3),
                 "reduction_after_backward_ms": round(max(0.0, last_done - bwd_end), 3),
                 "reduction_busy_ms": round(sum(r["end_ms"] - r["start_ms"] for r in rows), 3), "buckets": rows}

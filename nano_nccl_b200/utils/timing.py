@@ -24,7 +24,7 @@ class L2Flusher:
 
 
 def time_iterations(fn: Callable[[], None], iters: int, warmup: int, flush: Optional[Callable[[], None]] = None,
-                    pre: Optional[Callable[[], None]] = None) -> list[float]:
+                    pre: Optional[Callable[[], None]] = None, head_start_ms: float = 3.0) -> list[float]:
     """Times each of `iters` calls of fn() with CUDA events on the current stream; returns µs."""
     for _ in range(warmup):
         if flush:
@@ -35,6 +35,10 @@ def time_iterations(fn: Callable[[], None], iters: int, warmup: int, flush: Opti
     torch.cuda.synchronize()
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
     stops = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
+    # Keep the GPU busy for a few milliseconds first, so that the host enqueues the whole timed loop ahead of the
+    # device: otherwise a short kernel is timed from its start event to whenever the host gets round to launching
+    # it, and the figure measures the host (a bounded spin, not a wait on anything).
+    torch.cuda._sleep(int(head_start_ms * 1.9e6))
     for i in range(iters):
         if flush:
             flush()

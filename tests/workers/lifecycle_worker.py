@@ -28,7 +28,8 @@ MODE = sys.argv[1]
 
 
 def make(port_offset, **kw):
-    return Communicator.from_tcp("127.0.0.1", PORT + port_offset, RANK, SIZE, device=kw.pop("device", torch.cuda.current_device()),
+    # the device is named explicitly: a failed creation may leave another device current in this process
+    return Communicator.from_tcp("127.0.0.1", PORT + port_offset, RANK, SIZE, device=kw.pop("device", RANK % torch.cuda.device_count()),
                                  wait_timeout_us=15_000_000, **kw)
 
 
@@ -76,6 +77,7 @@ def same_device():
         assert "same CUDA device" in str(e), str(e)
     else:
         raise AssertionError(f"[rank {RANK}] two ranks on device 0 were accepted")
+    torch.cuda.set_device(RANK % torch.cuda.device_count())
     comm = make(1)   # with distinct devices everything is fine afterwards
     smoke(comm, 4096)
     comm.destroy()
