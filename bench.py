@@ -49,7 +49,7 @@ def parse_args():
     ap.add_argument("--model", default="gpt2-medium")
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--no-overlap", action="store_true")
-    ap.add_argument("--comm-ctas", type=int, default=8)
+    ap.add_argument("--comm-ctas", type=int, default=-1, help="CTAs of a gradient reduction beside backward (-1: the engine's default, 0: the tuner's grid)")
     ap.add_argument("--shard-optimizer", action="store_true",
                     help="optimizer-state sharding: ReduceScatter + AdamW on 1/N + AllGather instead of AllReduce + AdamW")
     ap.add_argument("--no-tail-full-grid", action="store_true",
@@ -157,7 +157,7 @@ def main() -> None:
         if world > 1:
             comm = Communicator.from_torch_distributed(device=local)
         engine = DataParallel(model, comm, bucket_bytes=25 * 1024 * 1024, overlap=not args.no_overlap,
-                              comm_ctas=args.comm_ctas, tail_full_grid=not args.no_tail_full_grid,
+                              comm_ctas=None if args.comm_ctas < 0 else args.comm_ctas, tail_full_grid=not args.no_tail_full_grid,
                               shard_optimizer=args.shard_optimizer)
 
         def train_step(idx, tgt):

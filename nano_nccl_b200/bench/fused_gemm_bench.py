@@ -4,10 +4,14 @@ Row-parallel:    activations 8192 x (14336/N) per rank times weight (14336/N) x 
 Column-parallel: AllGather of (8192/N) x 4096 token shards, GEMM with a 4096 x (14336/N) weight.
 Weights normal(0, 0.02), activations normal(0, 1), seeded.  5 warm-up + 20 timed iterations, CUDA events
 after an L2 flush and a device-side rank alignment, p50, max over ranks.  Roofline: the slower of
-FLOPs / measured bf16 GEMM peak and NVLink bytes / 770 GB/s (measured peer-copy bandwidth per direction).
+FLOPs / measured bf16 GEMM peak (1667.7 TFLOP/s) and NVLink bytes / 900 GB/s (nominal, per direction);
+`frac_of_roofline_measured_link` uses the bandwidth a push actually reaches on this pool instead.
 
 Usage: torchrun --nproc-per-node N -m nano_nccl_b200.bench.fused_gemm_bench [--out file.jsonl]
        python -m nano_nccl_b200.bench.fused_gemm_bench --plain     (1 GPU: tcgen05 GEMM vs cuBLAS)
+
+`--variants "default;NANO_NCCL_AG_PUSH_PARTS=8;NANO_NCCL_GEMM_RS_TMA=1"` times the fused kernels once per environment
+variant in the same process (the switches are read when the fused workspace is created); cuBLAS + NCCL is timed once.
 """
 from __future__ import annotations
 
@@ -22,7 +26,8 @@ from nano_nccl_b200.ops.gemm import FusedTensorParallel, gemm_bf16, gemm_last_er
 from nano_nccl_b200.utils.timing import L2Flusher, max_over_ranks, p50, time_iterations
 
 PEAK_TFLOPS = 1667.7      # measured cuBLAS bf16 burst on this pool
-NVLINK_GBS = 770.0        # measured peer copy per direction
+NVLINK_GBS = 900.0        # nominal NVLink 5 bandwidth per direction per GPU: the roofline constant
+NVLINK_MEASURED_GBS = 585.0  # what SM stores, TMA bulk copies and the copy engine all reach at 32 MiB (p2p_bandwidth)
 
 
 def plain(args) -> None:
@@ -56,6 +61,7 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--ffn", type=int, default=14336)
+    ap.add_argument("--variants", default="", help="';'-separated environment variants of the fused kernels")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
     if args.plain:
@@ -71,7 +77,9 @@ def main() -> None:
     comm = Communicator.from_torch_distributed(device=local)
     M, H, F = args.tokens, args.hidden, args.ffn
     Fp = F // world
-    tp = FusedTensorParallel(comm, M * H * 2, M * H * 2)
+    from nano_nccl_b200.bench.collective_sweep import apply_variant, restore_env
+
+    variants = [v.strip() for v in args.variants.split(";") if v.strip()] or ["default"]
     flush = L2Flusher()
     align = torch.zeros(1, device="cuda")
     torch.manual_seed(1234 + rank)
@@ -91,7 +99,21 @@ def main() -> None:
         torch.matmul(a, w.t(), out=partial)
         dist.reduce_scatter_tensor(ref_out, partial)
 
-    t_fused = max_over_ranks(p50(time_iterations(lambda: tp.gemm_rs(a, w, out), args.iters, args.warmup, flush=flush, pre=aligned)))
+    def fused_times(call):
+        """p50 of the fused op per variant: a workspace of its own per variant, destroyed afterwards."""
+        out_us = {}
+        for variant in variants:
+            saved = apply_variant(variant)
+            tp = FusedTensorParallel(comm, M * H * 2, M * H * 2)
+            restore_env(saved)
+            out_us[variant] = max_over_ranks(p50(time_iterations(lambda: call(tp), args.iters, args.warmup, flush=flush, pre=aligned)))
+            torch.cuda.synchronize()
+            assert gemm_last_error() == 0, (variant, gemm_last_error())
+            tp.destroy()
+        return out_us
+
+    rs_us = fused_times(lambda tp: tp.gemm_rs(a, w, out))
+    t_fused = rs_us[variants[0]]
     t_base = max_over_ranks(p50(time_iterations(baseline_rs, args.iters, args.warmup, flush=flush, pre=aligned)))
     t_gemm = max_over_ranks(p50(time_iterations(lambda: torch.matmul(a, w.t(), out=partial), args.iters, args.warmup, flush=flush)))
     assert gemm_last_error() == 0
@@ -99,10 +121,12 @@ def main() -> None:
     fl = 2.0 * M * H * Fp
     link_bytes = (world - 1) / world * M * H * 2
     roof_us = max(fl / (PEAK_TFLOPS * 1e6), link_bytes / (NVLINK_GBS * 1e3))
+    roof_meas = max(fl / (PEAK_TFLOPS * 1e6), link_bytes / (NVLINK_MEASURED_GBS * 1e3))
     rows.append({"op": "gemm_rs", "nranks": world, "M": M, "N": H, "K_per_rank": Fp, "fused_us": round(t_fused, 2),
                  "cublas_nccl_us": round(t_base, 2), "cublas_only_us": round(t_gemm, 2), "roofline_us": round(roof_us, 2),
-                 "frac_of_roofline": round(roof_us / t_fused, 3), "speedup_vs_cublas_nccl": round(t_base / t_fused, 3),
-                 "max_abs_diff_vs_baseline": round(err, 4)})
+                 "frac_of_roofline": round(roof_us / t_fused, 3), "frac_of_roofline_measured_link": round(roof_meas / t_fused, 3),
+                 "speedup_vs_cublas_nccl": round(t_base / t_fused, 3), "max_abs_diff_vs_baseline": round(err, 4),
+                 "variants_us": {k: round(v, 2) for k, v in rs_us.items()}})
     # ---- column-parallel: all-gather [M/world, H] shards -> [M, H] x [Fp, H]^T -> [M, Fp]
     x = torch.randn(M // world, H, device="cuda").bfloat16()
     w2 = (torch.randn(Fp, H, device="cuda") * 0.02).bfloat16()
@@ -114,17 +138,20 @@ def main() -> None:
         dist.all_gather_into_tensor(gathered, x)
         torch.matmul(gathered, w2.t(), out=ref2)
 
-    t_fused2 = max_over_ranks(p50(time_iterations(lambda: tp.ag_gemm(x, w2, out2), args.iters, args.warmup, flush=flush, pre=aligned)))
+    ag_us = fused_times(lambda tp: tp.ag_gemm(x, w2, out2))
+    t_fused2 = ag_us[variants[0]]
     t_base2 = max_over_ranks(p50(time_iterations(baseline_ag, args.iters, args.warmup, flush=flush, pre=aligned)))
     assert gemm_last_error() == 0
     err2 = (out2.float() - ref2.float()).abs().max().item()
     fl2 = 2.0 * M * H * Fp
     link2 = (world - 1) / world * M * H * 2
     roof2 = max(fl2 / (PEAK_TFLOPS * 1e6), link2 / (NVLINK_GBS * 1e3))
+    roof2_meas = max(fl2 / (PEAK_TFLOPS * 1e6), link2 / (NVLINK_MEASURED_GBS * 1e3))
     rows.append({"op": "ag_gemm", "nranks": world, "M": M, "N_per_rank": Fp, "K": H, "fused_us": round(t_fused2, 2),
                  "cublas_nccl_us": round(t_base2, 2), "roofline_us": round(roof2, 2),
-                 "frac_of_roofline": round(roof2 / t_fused2, 3), "speedup_vs_cublas_nccl": round(t_base2 / t_fused2, 3),
-                 "max_abs_diff_vs_baseline": round(err2, 4)})
+                 "frac_of_roofline": round(roof2 / t_fused2, 3), "frac_of_roofline_measured_link": round(roof2_meas / t_fused2, 3),
+                 "speedup_vs_cublas_nccl": round(t_base2 / t_fused2, 3), "max_abs_diff_vs_baseline": round(err2, 4),
+                 "variants_us": {k: round(v, 2) for k, v in ag_us.items()}})
     if rank == 0:
         for r in rows:
             print(json.dumps(r), flush=True)
@@ -133,7 +160,6 @@ def main() -> None:
             with open(args.out, "w") as f:
                 for r in rows:
                     f.write(json.dumps(r) + "\n")
-    tp.destroy()
     comm.destroy()
     dist.destroy_process_group()
 

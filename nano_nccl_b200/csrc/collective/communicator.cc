@@ -143,6 +143,7 @@ Communicator::Impl::Impl(std::shared_ptr<Bootstrap> bootstrap, const Communicato
     // take the software-pipelined kernels; 0 switches them off.
     pipe_min_bytes_ = static_cast<std::size_t>(env::integer("NANO_NCCL_PIPE_MIN_BYTES", 8 << 20, 0, 1ll << 40));
     pipe_tile_bytes_ = static_cast<std::size_t>(env::integer("NANO_NCCL_PIPE_TILE_BYTES", 0, 0, 1 << 20));
+    pipe_depth_ = static_cast<int>(env::integer("NANO_NCCL_PIPE_DEPTH", 0, 0, dev::kMaxPipeDepth));
     if (auto algo = env::get("NANO_NCCL_PIPE_ALGO")) {
         NANO_REQUIRE_ARG(parse_algo(algo->c_str(), &pipe_algo_) && (pipe_algo_ == AlgoKind::Auto || pipe_algo_ == AlgoKind::TwoShot || pipe_algo_ == AlgoKind::Nvls),
                          "NANO_NCCL_PIPE_ALGO must be auto, twoshot or nvls, got '%s'", algo->c_str());
@@ -419,12 +420,12 @@ void Communicator::Impl::all_reduce(const AllReduceArgs& a) {
         const bool through_switch = multicast_available() && adds &&
                                     (pipe_algo_ == AlgoKind::Nvls || (pipe_algo_ == AlgoKind::Auto && (nranks_ > 2 || d.algo == AlgoKind::Nvls)));
         if (through_switch) {
-            const dev::Geometry g = dev::make_pipe_geometry(dev::Family::ArNvls, a.count, dtype_size(a.dtype), nranks_, d.max_grid, pipe_tile_bytes_);
+            const dev::Geometry g = dev::make_pipe_geometry(dev::Family::ArNvls, a.count, dtype_size(a.dtype), nranks_, d.max_grid, pipe_tile_bytes_, pipe_depth_);
             err = dev::launch_ar_nvls_pipe(dev_, a.send_buffer, a.recv_buffer, a.count, a.dtype, a.redop, g, a.stream);
             ++stats_.nvls;
             last_algo_ = AlgoKind::Nvls;
         } else {
-            const dev::Geometry g = dev::make_pipe_geometry(dev::Family::ArTwoShot, a.count, dtype_size(a.dtype), nranks_, d.max_grid, pipe_tile_bytes_);
+            const dev::Geometry g = dev::make_pipe_geometry(dev::Family::ArTwoShot, a.count, dtype_size(a.dtype), nranks_, d.max_grid, pipe_tile_bytes_, pipe_depth_);
             err = dev::launch_ar_twoshot_pipe(dev_, a.send_buffer, a.recv_buffer, a.count, a.dtype, a.redop, push_multicast(), g, a.stream);
             ++stats_.twoshot;
             last_algo_ = AlgoKind::TwoShot;
@@ -511,7 +512,7 @@ void Communicator::Impl::reduce_scatter(const ReduceScatterArgs& a) {
         return;
     }
     if (pipe_min_bytes_ != 0 && bytes * nranks_ >= pipe_min_bytes_) {
-        const dev::Geometry g = dev::make_pipe_geometry(dev::Family::ReduceScatter, a.recv_count, dtype_size(a.dtype), nranks_, d.max_grid, pipe_tile_bytes_);
+        const dev::Geometry g = dev::make_pipe_geometry(dev::Family::ReduceScatter, a.recv_count, dtype_size(a.dtype), nranks_, d.max_grid, pipe_tile_bytes_, pipe_depth_);
         const cudaError_t e = dev::launch_rs_pipe(dev_, a.send_buffer, a.recv_buffer, a.recv_count, a.dtype, a.redop, g, a.stream);
         ++stats_.oneshot;
         ++stats_.pipelined;
@@ -578,7 +579,7 @@ void Communicator::Impl::all_gather(const AllGatherArgs& a) {
         return;
     }
     if (pipe_min_bytes_ != 0 && bytes * nranks_ >= pipe_min_bytes_ && !push_tma_) {
-        const dev::Geometry g = dev::make_pipe_geometry(dev::Family::AllGather, a.send_count, dtype_size(a.dtype), nranks_, d.max_grid, pipe_tile_bytes_);
+        const dev::Geometry g = dev::make_pipe_geometry(dev::Family::AllGather, a.send_count, dtype_size(a.dtype), nranks_, d.max_grid, pipe_tile_bytes_, pipe_depth_);
         const cudaError_t e = dev::launch_ag_pipe(dev_, a.send_buffer, a.recv_buffer, a.send_count, a.dtype, push_multicast(), g, a.stream);
         ++stats_.oneshot;
         ++stats_.pipelined;

@@ -66,7 +66,8 @@ public:
     int debug_level_ = 0;        // NANO_NCCL_DEBUG: unset / 0 = quiet, info = one line at creation, trace = one line per collective
     std::size_t tile_cap_ = 0;  // NANO_NCCL_TILE_BYTES: cap on the tile size (0: as large as staging allows)
     std::size_t pipe_min_bytes_ = 0;   // NANO_NCCL_PIPE_MIN_BYTES: smallest message of the software-pipelined kernels (0: off)
-    std::size_t pipe_tile_bytes_ = 0;  // NANO_NCCL_PIPE_TILE_BYTES: their tile size (0: a quarter of a CTA's region)
+    std::size_t pipe_tile_bytes_ = 0;  // NANO_NCCL_PIPE_TILE_BYTES: their tile size (0: a sixteenth of a CTA's region)
+    int pipe_depth_ = 0;               // NANO_NCCL_PIPE_DEPTH: iterations between a tile's stages (0: the built-in choice)
     AlgoKind pipe_algo_ = AlgoKind::Auto;  // NANO_NCCL_PIPE_ALGO: auto / twoshot / nvls for the pipelined AllReduce
     bool push_tma_ = false;  // NANO_NCCL_PUSH_TMA=1: AllGather pushes through TMA bulk copies (experimental)
     bool debug_signatures_ = false;  // NANO_NCCL_DEBUG_SIGNATURES=1: ranks compare descriptors before every call

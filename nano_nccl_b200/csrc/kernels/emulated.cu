@@ -26,6 +26,7 @@ struct EmulatedCluster::State {
     // software-pipelined kernels for messages of at least this size (NANO_NCCL_PIPE_MIN_BYTES when the cluster is created)
     std::size_t pipe_min_bytes = 0;
     std::size_t pipe_tile_bytes = 0;
+    int pipe_depth = 0;
 };
 
 namespace {
@@ -89,6 +90,7 @@ EmulatedCluster::EmulatedCluster(int device, int nranks, std::int64_t timeout_us
     s_->ll_max_bytes = static_cast<std::size_t>(env::integer("NANO_NCCL_LL_MAX_BYTES", 0, 0, 16 << 20));
     s_->pipe_min_bytes = static_cast<std::size_t>(env::integer("NANO_NCCL_PIPE_MIN_BYTES", 8 << 20, 0, 1ll << 40));
     s_->pipe_tile_bytes = static_cast<std::size_t>(env::integer("NANO_NCCL_PIPE_TILE_BYTES", 0, 0, 1 << 20));
+    s_->pipe_depth = static_cast<int>(env::integer("NANO_NCCL_PIPE_DEPTH", 0, 0, kMaxPipeDepth));
     if (s_->ll_max_bytes != 0) {
         LLDev l{};
         for (int r = 0; r < nranks; ++r) {
@@ -125,7 +127,7 @@ void EmulatedCluster::all_reduce(const void* const* srcs, void* const* dsts, std
     const Family fam = algo == AlgoKind::OneShot ? Family::ArOneShot : Family::ArTwoShot;
     const bool ll = algo == AlgoKind::OneShot && s_->ll_max_bytes != 0 && count * dtype_size(dtype) <= s_->ll_max_bytes;
     const bool pipe = algo == AlgoKind::TwoShot && s_->pipe_min_bytes != 0 && count * dtype_size(dtype) >= s_->pipe_min_bytes;
-    const Geometry g = pipe ? make_pipe_geometry(fam, count, dtype_size(dtype), nranks_, max_grid, s_->pipe_tile_bytes)
+    const Geometry g = pipe ? make_pipe_geometry(fam, count, dtype_size(dtype), nranks_, max_grid, s_->pipe_tile_bytes, s_->pipe_depth)
                             : make_geometry(fam, count, dtype_size(dtype), nranks_, max_grid, !ll, ll ? ll_tile_cap_bytes(nranks_) : 0);
     const EmuRanks* e = static_cast<const EmuRanks*>(s_->ranks_dev.data());
     const LLDev* l = static_cast<const LLDev*>(s_->ll_dev.data());
@@ -154,7 +156,7 @@ void EmulatedCluster::reduce_scatter(const void* const* srcs, void* const* dsts,
     upload(s_->ranks_host, s_->ranks_dev, srcs, dsts, nranks_, stream);
     const bool ll = s_->ll_max_bytes != 0 && recv_count * dtype_size(dtype) * nranks_ <= s_->ll_max_bytes;
     const bool pipe = s_->pipe_min_bytes != 0 && recv_count * dtype_size(dtype) * nranks_ >= s_->pipe_min_bytes;
-    const Geometry g = pipe ? make_pipe_geometry(Family::ReduceScatter, recv_count, dtype_size(dtype), nranks_, max_grid, s_->pipe_tile_bytes)
+    const Geometry g = pipe ? make_pipe_geometry(Family::ReduceScatter, recv_count, dtype_size(dtype), nranks_, max_grid, s_->pipe_tile_bytes, s_->pipe_depth)
                             : make_geometry(Family::ReduceScatter, recv_count, dtype_size(dtype), nranks_, max_grid, true,
                                             ll ? ll_tile_cap_bytes(nranks_) : 0);
     const EmuRanks* e = static_cast<const EmuRanks*>(s_->ranks_dev.data());
@@ -179,7 +181,7 @@ void EmulatedCluster::all_gather(const void* const* srcs, void* const* dsts, std
     const bool ll = s_->ll_max_bytes != 0 && send_count * dtype_size(dtype) * nranks_ <= s_->ll_max_bytes;
     const bool pipe = s_->pipe_min_bytes != 0 && send_count * dtype_size(dtype) * nranks_ >= s_->pipe_min_bytes &&
                       !env::flag("NANO_NCCL_PUSH_TMA", false);
-    const Geometry g = pipe ? make_pipe_geometry(Family::AllGather, send_count, dtype_size(dtype), nranks_, max_grid, s_->pipe_tile_bytes)
+    const Geometry g = pipe ? make_pipe_geometry(Family::AllGather, send_count, dtype_size(dtype), nranks_, max_grid, s_->pipe_tile_bytes, s_->pipe_depth)
                             : make_geometry(Family::AllGather, send_count, dtype_size(dtype), nranks_, max_grid, true,
                                             ll ? ll_tile_cap_bytes(nranks_) : 0);
     const EmuRanks* e = static_cast<const EmuRanks*>(s_->ranks_dev.data());

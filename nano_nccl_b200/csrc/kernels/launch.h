@@ -14,6 +14,12 @@ namespace nano_nccl::dev {
 // (first tile half-size), so that at any moment about half of the CTAs are in the egress-heavy
 // push phase while the others are in the ingress-heavy reduce / broadcast phase, instead of all
 // CTAs of all GPUs marching through the phases together.
+#if defined(__CUDACC__)
+#define NANO_GEOM_HD_EARLY __host__ __device__ inline
+#else
+#define NANO_GEOM_HD_EARLY inline
+#endif
+
 struct Geometry {
     int grid = 1;                   // CTAs
     std::size_t region_elems = 0;   // elements per CTA (multiple of the tile unit)
@@ -21,7 +27,14 @@ struct Geometry {
     int iters = 1;                  // tiles each CTA walks (padding tiles are empty)
     std::size_t slot_bytes = 0;     // staging bytes reserved per source rank (or per sub-slice)
     int skew = 0;
+    int depth = 0;                  // pipelined kernels: iterations between a tile's stages (buffers = 2 * depth + 1)
 };
+
+// Pipelined kernels: a CTA's 2 MiB of staging cut into 2 * depth + 1 buffers (multiples of 1 KiB).
+constexpr int kMaxPipeDepth = 8;
+NANO_GEOM_HD_EARLY std::size_t pipe_buf_bytes(int depth) {
+    return kBlockStageBytes / static_cast<std::size_t>(2 * depth + 1) / 1024 * 1024;
+}
 
 #if defined(__CUDACC__)
 #define NANO_GEOM_HD __host__ __device__ inline
@@ -111,7 +124,7 @@ cudaError_t launch_barrier(const CommDev& c, int grid, cudaStream_t stream);
 // Software-pipelined forms for large messages (kernels/pipelined.cuh): a CTA keeps three tiles in flight and
 // waits only for signals that are one iteration old.  `g` must come from make_pipe_geometry.
 Geometry make_pipe_geometry(Family family, std::size_t count, std::size_t elem_size, int nranks, int max_grid,
-                            std::size_t tile_bytes_hint = 0);
+                            std::size_t tile_bytes_hint = 0, int depth_hint = 0);
 cudaError_t launch_ar_twoshot_pipe(const CommDev& c, const void* src, void* dst, std::size_t count, DType dtype, RedOp op,
                                    bool multicast, const Geometry& g, cudaStream_t stream);
 cudaError_t launch_ar_nvls_pipe(const CommDev& c, const void* src, void* dst, std::size_t count, DType dtype, RedOp op,

@@ -6,33 +6,40 @@
 
 namespace nano_nccl::dev {
 
-// A CTA should walk at least four tiles, or the pipeline never fills; a tile below 32 KiB spends its time on
-// flags.  So the grid shrinks until a CTA's region holds four such tiles (never below 16 CTAs, which still
-// drive most of a link), and the tile is a quarter of the region, capped by what a pipeline buffer holds.
+// The tile is what a CTA moves per iteration; the depth D is how many iterations separate a tile's stages.
+// A signal (fence + flag flight) takes some 10 us on a busy link; an iteration moves one tile at the CTA's share of
+// the link (about 4.5 GB/s with 128 CTAs), i.e. 32 KiB in about 7 us.  So: tiles of a sixteenth of the CTA's
+// region, at least 16 KiB (8 KiB per rank for ReduceScatter / AllGather, whose staging holds one tile per rank)
+// and at most what a buffer holds; D = 4 unless a hint says otherwise; the grid shrinks (never below 16 CTAs)
+// until a region holds at least eight such tiles.
 Geometry make_pipe_geometry(Family family, std::size_t count, std::size_t elem_size, int nranks, int max_grid,
-                            std::size_t tile_bytes_hint) {
+                            std::size_t tile_bytes_hint, int depth_hint) {
     const std::size_t n = static_cast<std::size_t>(nranks);
+    const int depth = std::max(1, std::min(depth_hint != 0 ? depth_hint : 4, kMaxPipeDepth));
+    const std::size_t buf = pipe_buf_bytes(depth);
     std::size_t cap = 0;       // largest tile (bytes of the tiled dimension) a pipeline buffer holds
-    std::size_t floor_tile = 32 * 1024;
+    std::size_t floor_tile = 16 * 1024;
     switch (family) {
-        case Family::ArTwoShot: cap = std::min<std::size_t>(256 * 1024, (kPipeBufBytes / 2) / n / 16 * 16 * n); break;
-        case Family::ArNvls: cap = 512 * 1024; break;
+        case Family::ArTwoShot: cap = (buf / 2) / n / 16 * 16 * n; break;   // scatter half + gather half, N slots each
+        case Family::ArNvls: cap = buf / (16 * n) * (16 * n); break;
         default:  // ReduceScatter / AllGather: a buffer holds one tile per rank
-            cap = kPipeBufBytes / n / 256 * 256;
-            floor_tile = std::max<std::size_t>(8 * 1024, floor_tile / n);
+            cap = buf / n / 256 * 256;
+            floor_tile = std::max<std::size_t>(4 * 1024, floor_tile / n);
             break;
     }
     const std::size_t bytes = count * elem_size;
     int grid = std::max(1, std::min(max_grid, kMaxBlocks));
-    while (grid > 16 && bytes / static_cast<std::size_t>(grid) < 4 * floor_tile) grid /= 2;
-    std::size_t tile = tile_bytes_hint != 0 ? tile_bytes_hint : std::max(floor_tile, bytes / static_cast<std::size_t>(grid) / 4);
+    while (grid > 16 && bytes / static_cast<std::size_t>(grid) < 8 * floor_tile) grid /= 2;
+    std::size_t tile = tile_bytes_hint != 0 ? tile_bytes_hint : std::max(floor_tile, bytes / static_cast<std::size_t>(grid) / 16);
     tile = std::min(tile, cap);
-    return make_geometry(family, count, elem_size, nranks, grid, /*allow_skew=*/false, tile);
+    Geometry g = make_geometry(family, count, elem_size, nranks, grid, /*allow_skew=*/false, tile);
+    g.depth = depth;
+    return g;
 }
 
 cudaError_t launch_ar_twoshot_pipe(const CommDev& c, const void* src, void* dst, std::size_t count, DType dtype, RedOp op,
                                    bool multicast, const Geometry& g, cudaStream_t stream) {
-    if (static_cast<std::size_t>(c.nranks) * g.slot_bytes > kPipeBufBytes / 2) return cudaErrorInvalidValue;
+    if (g.depth < 1 || g.depth > kMaxPipeDepth || static_cast<std::size_t>(c.nranks) * g.slot_bytes > pipe_buf_bytes(g.depth) / 2) return cudaErrorInvalidValue;
     return dispatch_dtype(dtype, [&](auto t) {
         using T = decltype(t);
         return dispatch_op(op, [&](auto o) {
@@ -52,7 +59,7 @@ cudaError_t launch_ar_twoshot_pipe(const CommDev& c, const void* src, void* dst,
 cudaError_t launch_ar_nvls_pipe(const CommDev& c, const void* src, void* dst, std::size_t count, DType dtype, RedOp op,
                                 const Geometry& g, cudaStream_t stream) {
     if (c.stage_mc == nullptr || !(op == RedOp::Sum || op == RedOp::Avg)) return cudaErrorInvalidValue;
-    if (g.tile_elems * dtype_size(dtype) > kPipeBufBytes) return cudaErrorInvalidValue;
+    if (g.depth < 1 || g.depth > kMaxPipeDepth || g.tile_elems * dtype_size(dtype) > pipe_buf_bytes(g.depth)) return cudaErrorInvalidValue;
     return dispatch_dtype(dtype, [&](auto t) {
         using T = decltype(t);
         if (op == RedOp::Sum) {
@@ -68,7 +75,7 @@ cudaError_t launch_ar_nvls_pipe(const CommDev& c, const void* src, void* dst, st
 
 cudaError_t launch_rs_pipe(const CommDev& c, const void* src, void* dst, std::size_t recv_count, DType dtype, RedOp op,
                            const Geometry& g, cudaStream_t stream) {
-    if (static_cast<std::size_t>(c.nranks) * g.slot_bytes > kPipeBufBytes) return cudaErrorInvalidValue;
+    if (g.depth < 1 || g.depth > kMaxPipeDepth || static_cast<std::size_t>(c.nranks) * g.slot_bytes > pipe_buf_bytes(g.depth)) return cudaErrorInvalidValue;
     return dispatch_dtype(dtype, [&](auto t) {
         using T = decltype(t);
         return dispatch_op(op, [&](auto o) {
@@ -82,7 +89,7 @@ cudaError_t launch_rs_pipe(const CommDev& c, const void* src, void* dst, std::si
 
 cudaError_t launch_ag_pipe(const CommDev& c, const void* src, void* dst, std::size_t send_count, DType dtype,
                            bool multicast, const Geometry& g, cudaStream_t stream) {
-    if (static_cast<std::size_t>(c.nranks) * g.slot_bytes > kPipeBufBytes) return cudaErrorInvalidValue;
+    if (g.depth < 1 || g.depth > kMaxPipeDepth || static_cast<std::size_t>(c.nranks) * g.slot_bytes > pipe_buf_bytes(g.depth)) return cudaErrorInvalidValue;
     auto go = [&](auto t) {
         using T = decltype(t);
         if (multicast) {

@@ -6,15 +6,18 @@
 // barrier exposes a release fence plus a flag flight.  Here a CTA works on three tiles at once, one per
 // stage, and only ever waits for a signal that its peers sent one iteration earlier:
 //
-//   iteration k:   A(k)    push tile k                                   signal A(k)
-//                  C(k-2)  [wait B(k-2)]  copy tile k-2 out               (three-stage kernels)
-//                  B(k-1)  [wait A(k-1)]  reduce / broadcast tile k-1    signal B(k-1)
+//   iteration k:   A(k)     push tile k                                    signal A(k)
+//                  C(k-2D)  [wait B(k-2D)]  copy tile k-2D out              (three-stage kernels)
+//                  B(k-D)   [wait A(k-D)]   reduce / broadcast tile k-D    signal B(k-D)
 //
-// Tile k lives in staging buffer k mod 3 of the CTA (three buffers of kPipeBufBytes inside the CTA's
-// 2 MiB of staging).  Why three are enough: buffer k mod 3 is written again by the peers' A(k+3), which
-// they start after their iteration k+2, and that iteration waited for B(k) of every rank; what B writes
-// (the gather area) is written again by the peers' B(k+3) after they waited for A(k+3), which a rank
-// signals after its C(k).  Two-stage kernels (ReduceScatter, AllGather) wait for B(k-3) before A(k).
+// D (Geometry::depth) is how many iterations lie between a tile's stages: a signal costs a release fence (the
+// link has to drain what was queued before it) plus a flag flight, some 10 us on a busy link, and it is hidden
+// when D iterations of other work take at least that long.  Tile k lives in staging buffer k mod R, R = 2D + 1
+// buffers cut out of the CTA's 2 MiB of staging.  Why R are enough: buffer k mod R is written again by the
+// peers' A(k+R); before that, in iteration k+R-1, they waited for B(k+R-1-2D) = B(k) of every rank.  What B
+// writes (the gather area) is written again by the peers' B(k+R) after they waited for A(k+R), which a rank
+// signals after its C(k) (iteration k+2D < k+R).  Two-stage kernels (ReduceScatter, AllGather) wait for
+// B(k-R) before A(k).
 //
 // Signals are two monotonic counters per (CTA, peer): stream A in the ordinary pad row (the same words and
 // the same epoch counter as block_barrier, of which a signal is one half), stream B in a second row.  They
@@ -31,15 +34,14 @@
 
 namespace nano_nccl::dev {
 
-constexpr int kPipeDepth = 3;
-constexpr std::size_t kPipeBufBytes = 640 * 1024;
-static_assert(kPipeDepth * kPipeBufBytes <= kBlockStageBytes, "three pipeline buffers fit a CTA's staging");
 // Second flag row: word index of (block, rank) inside a rank's signal pads.  Below the fused-GEMM flags.
 constexpr std::size_t kPipeFlagRowWords = 2048;
 static_assert((kPipeFlagRowWords + kMaxBlocks * kPadWordsPerBlock) * 4 <= kGemmFlagOffsetBytes, "second flag row fits");
 
-__device__ __forceinline__ std::size_t pipe_buf_offset(int k) {
-    return static_cast<std::size_t>(blockIdx.x) * kBlockStageBytes + static_cast<std::size_t>(k % kPipeDepth) * kPipeBufBytes;
+// Buffer of tile k: one of the 2 * depth + 1 buffers of this CTA's staging.
+__device__ __forceinline__ std::size_t pipe_buf_offset(const Geometry& g, int k) {
+    return static_cast<std::size_t>(blockIdx.x) * kBlockStageBytes +
+           static_cast<std::size_t>(k % (2 * g.depth + 1)) * pipe_buf_bytes(g.depth);
 }
 
 // Roles inside a CTA: warps 0..14 (kPipeDataThreads) move data; warp 15 only signals.  A signal is a release
@@ -120,7 +122,7 @@ __device__ __forceinline__ bool pipe_signal_when_done(const CommDev& c, PipeShar
 // The schedule.  stage_a / stage_b / stage_c take the tile index and are run by the data threads (they must
 // stride by kPipeDataThreads); kThree selects the three-stage form.
 template <bool kThree, typename FA, typename FB, typename FC>
-__device__ __forceinline__ void pipe_run(const CommDev& c, int tiles, FA&& stage_a, FB&& stage_b, FC&& stage_c) {
+__device__ __forceinline__ void pipe_run(const CommDev& c, int tiles, int D, FA&& stage_a, FB&& stage_b, FC&& stage_c) {
     __shared__ PipeShared sh;
     std::uint32_t epoch = c.state[blockIdx.x].epoch;
     std::uint32_t epoch_b = c.state[blockIdx.x].epoch_b;
@@ -137,33 +139,34 @@ __device__ __forceinline__ void pipe_run(const CommDev& c, int tiles, FA&& stage
     }
     bool ok = block_barrier(c, epoch, 1);  // also publishes the shared-memory set-up to every warp
     const std::uint32_t a0 = epoch, b0 = epoch_b;  // signal A(k) carries a0 + k + 1, signal B(k) carries b0 + k + 1
-    const int last = tiles + (kThree ? 1 : 0);
+    const int R = 2 * D + 1;                                   // buffers
+    const int last = tiles - 1 + (kThree ? 2 * D : D);         // last iteration with work
     if (ok && threadIdx.x >= kPipeDataThreads) {
         // ---- signalling warp: the data warps' hand-overs in their program order
         for (int k = 0; k <= last; ++k) {
             if (k < tiles && !pipe_signal_when_done(c, sh, &sh.bar_a, &sh.taken_a, static_cast<std::uint32_t>(k), 0,
                                                     a0 + static_cast<std::uint32_t>(k) + 1u)) break;
-            if (k >= 1 && k - 1 < tiles &&
-                !pipe_signal_when_done(c, sh, &sh.bar_b, &sh.taken_b, static_cast<std::uint32_t>(k - 1), kPipeFlagRowWords,
-                                       b0 + static_cast<std::uint32_t>(k))) break;
+            if (k >= D && k - D < tiles &&
+                !pipe_signal_when_done(c, sh, &sh.bar_b, &sh.taken_b, static_cast<std::uint32_t>(k - D), kPipeFlagRowWords,
+                                       b0 + static_cast<std::uint32_t>(k - D) + 1u)) break;
         }
     } else if (ok) {
         // ---- data warps
         for (int k = 0; k <= last; ++k) {
             if (k < tiles) {
-                if (!kThree && k >= kPipeDepth &&
-                    !pipe_wait(c, sh, kPipeFlagRowWords, b0 + static_cast<std::uint32_t>(k - kPipeDepth) + 1u, 3)) break;
+                // two-stage kernels: the buffer is free once every peer has consumed the tile that used it last
+                if (!kThree && k >= R && !pipe_wait(c, sh, kPipeFlagRowWords, b0 + static_cast<std::uint32_t>(k - R) + 1u, 3)) break;
                 stage_a(k);
                 pipe_hand_over(c, sh, &sh.bar_a, &sh.taken_a, static_cast<std::uint32_t>(k));
             }
-            if (kThree && k >= 2 && k - 2 < tiles) {
-                if (!pipe_wait(c, sh, kPipeFlagRowWords, b0 + static_cast<std::uint32_t>(k - 2) + 1u, 4)) break;
-                stage_c(k - 2);
+            if (kThree && k >= 2 * D && k - 2 * D < tiles) {
+                if (!pipe_wait(c, sh, kPipeFlagRowWords, b0 + static_cast<std::uint32_t>(k - 2 * D) + 1u, 4)) break;
+                stage_c(k - 2 * D);
             }
-            if (k >= 1 && k - 1 < tiles) {
-                if (!pipe_wait(c, sh, 0, a0 + static_cast<std::uint32_t>(k), 3)) break;
-                stage_b(k - 1);
-                pipe_hand_over(c, sh, &sh.bar_b, &sh.taken_b, static_cast<std::uint32_t>(k - 1));
+            if (k >= D && k - D < tiles) {
+                if (!pipe_wait(c, sh, 0, a0 + static_cast<std::uint32_t>(k - D) + 1u, 3)) break;
+                stage_b(k - D);
+                pipe_hand_over(c, sh, &sh.bar_b, &sh.taken_b, static_cast<std::uint32_t>(k - D));
             }
         }
     }
@@ -209,7 +212,7 @@ template <typename T, RedOp Op, bool kMc>
 __device__ __forceinline__ void
 ar_twoshot_pipe_body(const CommDev& c, const T* src, T* dst, std::size_t count, const Geometry g) {
     constexpr int kE = ElemsPerVec<T>::value;
-    constexpr std::size_t kGatherOff = kPipeBufBytes / 2;
+    const std::size_t kGatherOff = pipe_buf_bytes(g.depth) / 2;
     const float inv = 1.0f / static_cast<float>(c.nranks);
     const int N = c.nranks;
     auto tile = [&](int k, std::size_t* t0, std::size_t* n) { tile_range(count, g, k, t0, n); };
@@ -217,7 +220,7 @@ ar_twoshot_pipe_body(const CommDev& c, const T* src, T* dst, std::size_t count, 
         std::size_t t0, n;
         tile(k, &t0, &n);
         if (!tile_fits(c, max_split_bytes<T>(n, N), g.slot_bytes, N, kGatherOff)) return;
-        const std::size_t off = pipe_buf_offset(k);
+        const std::size_t off = pipe_buf_offset(g, k);
         const T* s = src + t0;
         const bool s_al = aligned16(s);
         for (int i = 1; i < N; ++i) {
@@ -233,7 +236,7 @@ ar_twoshot_pipe_body(const CommDev& c, const T* src, T* dst, std::size_t count, 
         std::size_t t0, n;
         tile(k, &t0, &n);
         if (!tile_fits(c, max_split_bytes<T>(n, N), g.slot_bytes, N, kGatherOff)) return;
-        const std::size_t off = pipe_buf_offset(k);
+        const std::size_t off = pipe_buf_offset(g, k);
         const T* s = src + t0;
         T* d = dst + t0;
         const bool s_al = aligned16(s), d_al = aligned16(d);
@@ -261,7 +264,7 @@ ar_twoshot_pipe_body(const CommDev& c, const T* src, T* dst, std::size_t count, 
     auto stage_c = [&](int k) {  // the other owners' results leave my gather half
         std::size_t t0, n;
         tile(k, &t0, &n);
-        const std::size_t off = pipe_buf_offset(k);
+        const std::size_t off = pipe_buf_offset(g, k);
         T* d = dst + t0;
         const bool d_al = aligned16(d);
         for (int i = 1; i < N; ++i) {
@@ -273,7 +276,7 @@ ar_twoshot_pipe_body(const CommDev& c, const T* src, T* dst, std::size_t count, 
                          [&](std::size_t v, const Vec16& x) { store_guarded(d + b, v * kE, len, d_al, x); });
         }
     };
-    pipe_run<true>(c, g.iters, stage_a, stage_b, stage_c);
+    pipe_run<true>(c, g.iters, g.depth, stage_a, stage_b, stage_c);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -290,8 +293,8 @@ ar_nvls_pipe_body(const CommDev& c, const T* src, T* dst, std::size_t count, con
         std::size_t t0, n;
         tile_range(count, g, k, &t0, &n);
         const std::size_t nvec = (n + kE - 1) / kE;
-        if (!tile_fits(c, nvec * 16, kPipeBufBytes, 1, kPipeBufBytes)) return;
-        char* mine = c.stage[c.rank] + pipe_buf_offset(k);
+        if (!tile_fits(c, nvec * 16, pipe_buf_bytes(g.depth), 1, pipe_buf_bytes(g.depth))) return;
+        char* mine = c.stage[c.rank] + pipe_buf_offset(g, k);
         const T* s = src + t0;
         const bool s_al = aligned16(s);
         batched_copy(nvec, [&](std::size_t v) { return load_guarded(s, v * kE, n, s_al); },
@@ -301,8 +304,8 @@ ar_nvls_pipe_body(const CommDev& c, const T* src, T* dst, std::size_t count, con
         std::size_t t0, n;
         tile_range(count, g, k, &t0, &n);
         const std::size_t nvec = (n + kE - 1) / kE;
-        if (!tile_fits(c, nvec * 16, kPipeBufBytes, 1, kPipeBufBytes)) return;
-        const std::size_t off = pipe_buf_offset(k);
+        if (!tile_fits(c, nvec * 16, pipe_buf_bytes(g.depth), 1, pipe_buf_bytes(g.depth))) return;
+        const std::size_t off = pipe_buf_offset(g, k);
         T* d = dst + t0;
         const bool d_al = aligned16(d);
         const std::size_t b = split_begin(n, N, c.rank, kE), e = split_begin(n, N, c.rank + 1, kE);
@@ -322,7 +325,7 @@ ar_nvls_pipe_body(const CommDev& c, const T* src, T* dst, std::size_t count, con
         std::size_t t0, n;
         tile_range(count, g, k, &t0, &n);
         const std::size_t nvec = (n + kE - 1) / kE;
-        const char* mine = c.stage[c.rank] + pipe_buf_offset(k);
+        const char* mine = c.stage[c.rank] + pipe_buf_offset(g, k);
         T* d = dst + t0;
         const bool d_al = aligned16(d);
         const std::size_t b = split_begin(n, N, c.rank, kE), e = split_begin(n, N, c.rank + 1, kE);
@@ -332,7 +335,7 @@ ar_nvls_pipe_body(const CommDev& c, const T* src, T* dst, std::size_t count, con
         batched_copy(rest, [&](std::size_t v) { return ld_vec_volatile(mine + (v < vb ? v : v + (ve - vb)) * 16); },
                      [&](std::size_t v, const Vec16& x) { store_guarded(d, (v < vb ? v : v + (ve - vb)) * kE, n, d_al, x); });
     };
-    pipe_run<true>(c, g.iters, stage_a, stage_b, stage_c);
+    pipe_run<true>(c, g.iters, g.depth, stage_a, stage_b, stage_c);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -347,8 +350,8 @@ rs_pipe_body(const CommDev& c, const T* src, T* dst, std::size_t count, const Ge
         std::size_t t0, n;
         tile_range(count, g, k, &t0, &n);
         const std::size_t nvec = (n + kE - 1) / kE;
-        if (!tile_fits(c, nvec * 16, g.slot_bytes, N, kPipeBufBytes)) return;
-        const std::size_t off = pipe_buf_offset(k);
+        if (!tile_fits(c, nvec * 16, g.slot_bytes, N, pipe_buf_bytes(g.depth))) return;
+        const std::size_t off = pipe_buf_offset(g, k);
         for (int i = 1; i < N; ++i) {
             const int j = (c.rank + i) % N;
             const T* s = src + static_cast<std::size_t>(j) * count + t0;
@@ -362,12 +365,12 @@ rs_pipe_body(const CommDev& c, const T* src, T* dst, std::size_t count, const Ge
         std::size_t t0, n;
         tile_range(count, g, k, &t0, &n);
         const std::size_t nvec = (n + kE - 1) / kE;
-        if (!tile_fits(c, nvec * 16, g.slot_bytes, N, kPipeBufBytes)) return;
+        if (!tile_fits(c, nvec * 16, g.slot_bytes, N, pipe_buf_bytes(g.depth))) return;
         const T* own = src + static_cast<std::size_t>(c.rank) * count + t0;
         const bool own_al = aligned16(own);
         T* d = dst + t0;
         const bool d_al = aligned16(d);
-        const char* in = c.stage[c.rank] + pipe_buf_offset(k);
+        const char* in = c.stage[c.rank] + pipe_buf_offset(g, k);
         for (std::size_t v = threadIdx.x; v < nvec; v += kPipeDataThreads) {
             Acc<T> acc;
             for (int r = 0; r < N; ++r) {
@@ -379,7 +382,7 @@ rs_pipe_body(const CommDev& c, const T* src, T* dst, std::size_t count, const Ge
             store_guarded(d, v * kE, n, d_al, pack<T>(acc));
         }
     };
-    pipe_run<false>(c, g.iters, stage_a, stage_b, [](int) {});
+    pipe_run<false>(c, g.iters, g.depth, stage_a, stage_b, [](int) {});
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -393,8 +396,8 @@ ag_pipe_body(const CommDev& c, const T* src, T* dst, std::size_t count, const Ge
         std::size_t t0, n;
         tile_range(count, g, k, &t0, &n);
         const std::size_t nvec = (n + kE - 1) / kE;
-        if (!tile_fits(c, nvec * 16, g.slot_bytes, N, kPipeBufBytes)) return;
-        const std::size_t off = pipe_buf_offset(k) + c.rank * g.slot_bytes;
+        if (!tile_fits(c, nvec * 16, g.slot_bytes, N, pipe_buf_bytes(g.depth))) return;
+        const std::size_t off = pipe_buf_offset(g, k) + c.rank * g.slot_bytes;
         const T* s = src + t0;
         const bool s_al = aligned16(s);
         T* own = dst + static_cast<std::size_t>(c.rank) * count + t0;
@@ -413,8 +416,8 @@ ag_pipe_body(const CommDev& c, const T* src, T* dst, std::size_t count, const Ge
         std::size_t t0, n;
         tile_range(count, g, k, &t0, &n);
         const std::size_t nvec = (n + kE - 1) / kE;
-        if (!tile_fits(c, nvec * 16, g.slot_bytes, N, kPipeBufBytes)) return;
-        const std::size_t off = pipe_buf_offset(k);
+        if (!tile_fits(c, nvec * 16, g.slot_bytes, N, pipe_buf_bytes(g.depth))) return;
+        const std::size_t off = pipe_buf_offset(g, k);
         for (int i = 1; i < N; ++i) {
             const int j = (c.rank + i) % N;
             T* d = dst + static_cast<std::size_t>(j) * count + t0;
@@ -424,7 +427,7 @@ ag_pipe_body(const CommDev& c, const T* src, T* dst, std::size_t count, const Ge
                          [&](std::size_t v, const Vec16& x) { store_guarded(d, v * kE, n, d_al, x); });
         }
     };
-    pipe_run<false>(c, g.iters, stage_a, stage_b, [](int) {});
+    pipe_run<false>(c, g.iters, g.depth, stage_a, stage_b, [](int) {});
 }
 
 // ------------------------------------------------------------------------------------------------
