@@ -7,7 +7,7 @@
     python -m nano_nccl_b200.bench.profile_cases emu_ll      # 8 emulated ranks, 256 KiB flag-in-data AllReduce
     python -m nano_nccl_b200.bench.profile_cases gemm_rs_single | ag_gemm_single   # fused GEMM kernels, one rank, 8192 x 4096 x 1792
 
-Messages of 8 MiB and more take the software-pipelined kernels (NANO_NCCL_PIPE_MIN_BYTES=0 selects the plain ones).
+NANO_NCCL_PIPE_MIN_BYTES=1048576 selects the software-pipelined kernels for these cases (default: the plain kernels).
 
 Each case also prints its CUDA-event time so the capture can be compared with an unprofiled run.
 """

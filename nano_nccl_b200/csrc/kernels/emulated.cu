@@ -88,7 +88,7 @@ EmulatedCluster::EmulatedCluster(int device, int nranks, std::int64_t timeout_us
     }
     s_->ranks_dev = RawDeviceBuffer(device, sizeof(EmuRanks));
     s_->ll_max_bytes = static_cast<std::size_t>(env::integer("NANO_NCCL_LL_MAX_BYTES", 0, 0, 16 << 20));
-    s_->pipe_min_bytes = static_cast<std::size_t>(env::integer("NANO_NCCL_PIPE_MIN_BYTES", 8 << 20, 0, 1ll << 40));
+    s_->pipe_min_bytes = static_cast<std::size_t>(env::integer("NANO_NCCL_PIPE_MIN_BYTES", 0, 0, 1ll << 40));
     s_->pipe_tile_bytes = static_cast<std::size_t>(env::integer("NANO_NCCL_PIPE_TILE_BYTES", 0, 0, 1 << 20));
     s_->pipe_depth = static_cast<int>(env::integer("NANO_NCCL_PIPE_DEPTH", 0, 0, kMaxPipeDepth));
     if (s_->ll_max_bytes != 0) {

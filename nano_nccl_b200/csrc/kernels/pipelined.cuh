@@ -26,6 +26,11 @@
 // halves: the first keeps the pushes away from a peer that is still copying out of the previous kernel's
 // half, the last lets the next kernel write anywhere.  All waits are bounded like everywhere else.
 //
+// Status: opt-in (NANO_NCCL_PIPE_MIN_BYTES).  On two B200 every configuration tried was slower than the plain
+// kernels: a signal is a release fence of about 5 us while the link is busy, the signalling warp issues two per
+// iteration one after the other, and so an iteration costs about 10 us however small the tile is.  More
+// signalling warps (fences in flight together, flags raised with a remote max) are the next step.
+//
 // The reference pipelines its ring the same way in spirit (up to four slices in flight per edge:
 // src/kernels/ring_simple_kernel.cuh:1116-1438); this is that idea on one- and two-hop algorithms.
 #pragma once
