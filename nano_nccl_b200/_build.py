@@ -79,7 +79,7 @@ def _deps_changed(dep_file: Path, target: Path) -> bool:
     return False
 
 
-def compile_one(src: Path, extra: list[str], tag: str, verbose: bool) -> Path:
+def compile_one(src: Path, extra: list[str], tag: str, verbose: bool, cxx: str | None = None) -> Path:
     """Compiles one translation unit; returns the object path."""
     rel = src.relative_to(CSRC)
     obj = OBJ / tag / rel.with_suffix(rel.suffix + ".o")
@@ -92,7 +92,7 @@ def compile_one(src: Path, extra: list[str], tag: str, verbose: bool) -> Path:
         cmd = [CC, "-O2", "-std=c11", "-fPIC", "-Wall", "-I", str(CUDA_HOME / "include")] + INCLUDES + extra + [
             "-MD", "-MF", str(dep), "-c", str(src), "-o", str(obj)]
     else:
-        cmd = [CXX] + CXX_FLAGS + extra + ["-MD", "-MF", str(dep), "-c", str(src), "-o", str(obj)]
+        cmd = [cxx or CXX] + CXX_FLAGS + extra + ["-MD", "-MF", str(dep), "-c", str(src), "-o", str(obj)]
     digest = hashlib.sha1(" ".join(cmd).encode()).hexdigest()
     if stamp.exists() and stamp.read_text() == digest and not _deps_changed(dep, obj):
         return obj
@@ -101,9 +101,9 @@ def compile_one(src: Path, extra: list[str], tag: str, verbose: bool) -> Path:
     return obj
 
 
-def _compile_many(sources: list[Path], extra: list[str], tag: str, verbose: bool, jobs: int) -> list[Path]:
+def _compile_many(sources: list[Path], extra: list[str], tag: str, verbose: bool, jobs: int, cxx: str | None = None) -> list[Path]:
     with ThreadPoolExecutor(max_workers=jobs) as pool:
-        return list(pool.map(lambda s: compile_one(s, extra, tag, verbose), sources))
+        return list(pool.map(lambda s: compile_one(s, extra, tag, verbose, cxx), sources))
 
 
 def _link(objs: list[Path], out: Path, flags: list[str], verbose: bool, shared: bool) -> None:
@@ -229,6 +229,61 @@ def build_programs(verbose: bool = False, jobs: int | None = None) -> list[Path]
     return outs
 
 
+SANITIZER_FLAGS = {"address": ["-fsanitize=address,undefined"], "thread": ["-fsanitize=thread"]}
+# Host-only translation units (no kernels) and the native tests that need nothing else: the proxies, the bootstraps,
+# the verbs providers, shared-memory regions, the CPU ring.
+SANITIZED_DIRS = ["core", "bootstrap", "transport/socket", "transport/rdma", "transport/shm"]
+SANITIZED_EXTRA = ["collective/host_ring.cc", "collective/signature.cc", "collective/tuner.cc"]
+SANITIZED_TESTS = ["socket_protocol_test", "bootstrap_test", "rdma_proxy_test", "host_ring_test", "rdma_ibv_contract_test"]
+
+
+def sanitizer_compiler(kind: str) -> str | None:
+    """A C++ compiler that can link with the sanitizer's run-time library: $CXX if it can, else the system g++ / clang++;
+    None when none of them can."""
+    import tempfile
+
+    with tempfile.TemporaryDirectory() as tmp:
+        src = Path(tmp) / "probe.cc"
+        src.write_text("int main() { return 0; }\n")
+        for cxx in dict.fromkeys([CXX, "/usr/bin/g++", "g++", "clang++"]):
+            if shutil.which(cxx) is None:
+                continue
+            if subprocess.run([cxx] + SANITIZER_FLAGS[kind] + [str(src), "-o", str(Path(tmp) / "probe")],
+                              capture_output=True).returncode == 0:
+                return cxx
+    return None
+
+
+def build_sanitized(kind: str, verbose: bool = False, jobs: int | None = None) -> list[Path]:
+    """The host-side native tests rebuilt with AddressSanitizer + UndefinedBehaviorSanitizer (kind "address") or
+    ThreadSanitizer (kind "thread"): sources compiled straight into the test programs, no shared library, no device
+    code.  The stand-in for a GPU memory checker on the host side of the library (proxy threads, bootstraps, the
+    verbs providers, the CPU ring); the reference has no sanitizer targets (its CMake files define none)."""
+    jobs = jobs or max(1, (os.cpu_count() or 4))
+    cxx = sanitizer_compiler(kind)
+    if cxx is None:
+        raise RuntimeError(f"no C++ compiler on this machine links with -fsanitize={kind}")
+    flags = SANITIZER_FLAGS[kind] + ["-O1", "-fno-omit-frame-pointer", "-I", str(CSRC / "minimpi")]
+    sources: list[Path] = []
+    for d in SANITIZED_DIRS:
+        sources += sorted((CSRC / d).glob("*.cc"))
+    sources += [CSRC / rel for rel in SANITIZED_EXTRA]
+    tag = "san_" + kind
+    objs = _compile_many(sources, flags, tag, verbose, jobs, cxx=cxx)
+    tests = [CSRC / "tests" / (name + ".cc") for name in SANITIZED_TESTS]
+    test_objs = _compile_many(tests, flags, tag, verbose, jobs, cxx=cxx)
+    outs = []
+    for src, obj in zip(tests, test_objs):
+        exe = LIB / "tests" / "san" / f"{src.stem}_{kind}"
+        exe.parent.mkdir(parents=True, exist_ok=True)
+        cmd = [cxx] + SANITIZER_FLAGS[kind] + ["-o", str(exe), str(obj)] + [str(o) for o in objs] + [
+            "-L", str(CUDA_HOME / "lib64"), "-lcudart", "-ldl", "-lpthread", "-lrt", "-Wl,-rpath," + str(CUDA_HOME / "lib64")]
+        if not exe.exists() or any(o.stat().st_mtime > exe.stat().st_mtime for o in objs + [obj]):
+            _run(cmd, verbose)
+        outs.append(exe)
+    return outs
+
+
 def torch_flags() -> tuple[list[str], list[str]]:
     import sysconfig
 
@@ -273,6 +328,10 @@ def build_all(verbose: bool = False, with_torch: bool = True) -> dict[str, objec
 
 
 if __name__ == "__main__":
+    if "--sanitize" in sys.argv:
+        for exe in build_sanitized(sys.argv[sys.argv.index("--sanitize") + 1], verbose="-q" not in sys.argv):
+            print("built", exe)
+        sys.exit(0)
     if "--install" in sys.argv:
         where = install(Path(sys.argv[sys.argv.index("--install") + 1]), verbose="-q" not in sys.argv)
         for k, v in where.items():

@@ -190,7 +190,11 @@ int main() {
             engine.add_send(e.sp.get());
             engine.start();
             CHECK(engine.thread_count() == (shared ? 1 : 2));
+#if !defined(__SANITIZE_THREAD__)   // the thread sanitizer runs a thread of its own, which the process-wide count would see
             CHECK(thread_count() == before + (shared ? 1 : 2));
+#else
+            (void)before;
+#endif
             for (int s = 0; s < 12; ++s) {  // three FIFO generations with the consumer keeping up
                 CHECK(wait_for([&] { return simple::host_load_step(&e.src.head) + kFifoSteps >= std::uint64_t(s) * 2 + 2; }));
                 e.produce(s * 2, 1024, static_cast<char>('a' + s));
@@ -201,7 +205,9 @@ int main() {
             CHECK(wait_for([&] { return e.sp->drained(); }));
             engine.stop();
             // a joined thread can stay listed under /proc/self/task for a moment after join() returns
+#if !defined(__SANITIZE_THREAD__)
             CHECK(wait_for([&] { return thread_count() == before; }));
+#endif
             CHECK(!e.errors.has_error());
         }
     }

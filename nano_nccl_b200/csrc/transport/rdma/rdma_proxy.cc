@@ -48,7 +48,8 @@ bool RdmaGdrReceiveFlush::flush(std::string* error) {
 RdmaSendProxy::RdmaSendProxy(ProxyIdentity id, ProxyFifo fifo, QueuePair* qp, MemoryRegion* fifo_mr,
                              AsyncErrorState* errors, RdmaProxyOptions options, volatile RdmaCtsSlot* cts)
     : id_(id), fifo_(fifo), qp_(qp), mr_(fifo_mr), errors_(errors), options_(options), cts_(cts) {
-    next_post_ = completed_ = host_load_step(fifo_.head);
+    next_post_ = host_load_step(fifo_.head);
+    completed_.store(next_post_, std::memory_order_relaxed);
     timeline_.enable(options.timeline);
     NANO_REQUIRE_ARG(!options.use_write || cts != nullptr, "the WRITE data plane needs a CTS FIFO");
 }
@@ -65,13 +66,17 @@ void RdmaSendProxy::fail(std::uint64_t step, const std::string& reason) {
 void RdmaSendProxy::retire_through(std::uint64_t step) {
     // RC completes in order: everything up to `step` is done, posted or elided.
     while (!inflight_.empty() && inflight_.front().step <= step) {
-        completed_ = inflight_.front().step + simple::kSliceSteps;
+        completed_.store(inflight_.front().step + simple::kSliceSteps, std::memory_order_release);
         inflight_.pop_front();
+        inflight_count_.store(inflight_.size(), std::memory_order_release);
     }
 }
 
+// Callable from any thread (teardown asks while the progress thread still runs): reads the published counters only.
 bool RdmaSendProxy::drained() const {
-    return failed_ || (inflight_.empty() && host_load_step(fifo_.tail) <= completed_);
+    return failed_.load(std::memory_order_acquire) ||
+           (inflight_count_.load(std::memory_order_acquire) == 0 &&
+            host_load_step(fifo_.tail) <= completed_.load(std::memory_order_acquire));
 }
 
 bool RdmaSendProxy::progress() {
@@ -88,6 +93,7 @@ bool RdmaSendProxy::progress() {
             if (bytes == 0) {
                 // zero-byte branch: nothing goes to the NIC
                 inflight_.push_back({next_post_, false});
+                inflight_count_.store(inflight_.size(), std::memory_order_release);
                 ++zero_payload_posts_;
             } else {
                 const bool more = tail >= next_post_ + 2 * simple::kSliceSteps &&
@@ -106,6 +112,7 @@ bool RdmaSendProxy::progress() {
                     qp_->post_send(next_post_, sge, signaled, false);
                 }
                 inflight_.push_back({next_post_, true});
+                inflight_count_.store(inflight_.size(), std::memory_order_release);
                 ++posts_;
                 if (signaled) ++signaled_posts_;
                 timeline_.depth(TimelineDepth::Inflight, static_cast<unsigned>(inflight_.size()));
@@ -115,8 +122,9 @@ bool RdmaSendProxy::progress() {
         }
         // ---- zero-byte slices at the head of the completion order retire on the host
         while (!inflight_.empty() && !inflight_.front().posted) {
-            completed_ = inflight_.front().step + simple::kSliceSteps;
+            completed_.store(inflight_.front().step + simple::kSliceSteps, std::memory_order_release);
             inflight_.pop_front();
+            inflight_count_.store(inflight_.size(), std::memory_order_release);
             moved = true;
         }
         // ---- harvest completions
@@ -133,10 +141,12 @@ bool RdmaSendProxy::progress() {
             }
         }
         while (!inflight_.empty() && !inflight_.front().posted) {
-            completed_ = inflight_.front().step + simple::kSliceSteps;
+            completed_.store(inflight_.front().step + simple::kSliceSteps, std::memory_order_release);
             inflight_.pop_front();
+            inflight_count_.store(inflight_.size(), std::memory_order_release);
         }
-        if (host_load_step(fifo_.head) != completed_) host_store_step(fifo_.head, completed_);
+        const std::uint64_t done = completed_.load(std::memory_order_relaxed);
+        if (host_load_step(fifo_.head) != done) host_store_step(fifo_.head, done);
     } catch (const std::exception& e) {
         fail(next_post_, e.what());
         return true;

@@ -104,11 +104,12 @@ private:
     AsyncErrorState* errors_;
     RdmaProxyOptions options_;
     volatile RdmaCtsSlot* cts_;
-    std::deque<Flight> inflight_;
+    std::deque<Flight> inflight_;                  // touched by the progress thread only
+    std::atomic<std::size_t> inflight_count_{0};   // its size, for drained() on another thread
     std::uint64_t next_post_ = 0;
-    std::uint64_t completed_ = 0;
+    std::atomic<std::uint64_t> completed_{0};      // written by the progress thread, read by drained()
     std::uint64_t posts_ = 0, zero_payload_posts_ = 0, signaled_posts_ = 0;
-    bool failed_ = false;
+    std::atomic<bool> failed_{false};
     RdmaProxyTimeline timeline_;
 };
 
@@ -146,7 +147,7 @@ private:
     std::uint64_t next_post_ = 0;   // next step to grant / pre-post
     std::uint64_t next_done_ = 0;   // next step expected to complete
     std::uint64_t received_ = 0, cts_posts_ = 0, cts_inline_posts_ = 0;
-    bool failed_ = false;
+    std::atomic<bool> failed_{false};
 };
 
 // Drives proxies: one shared thread (receives first, then sends, pause when idle) or one thread

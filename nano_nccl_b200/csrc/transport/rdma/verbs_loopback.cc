@@ -55,7 +55,11 @@ private:
 
 class LoopbackQp;
 std::mutex g_qp_registry_mutex;
-std::map<std::uint32_t, LoopbackQp*> g_qp_registry;
+// Never destroyed: a progress thread may still look a peer up while the process runs its exit handlers.
+std::map<std::uint32_t, LoopbackQp*>& qp_registry() {
+    static auto* registry = new std::map<std::uint32_t, LoopbackQp*>();
+    return *registry;
+}
 
 class LoopbackQp final : public QueuePair {
 public:
@@ -63,11 +67,11 @@ public:
         : fabric_(std::move(f)), send_depth_(send_depth), recv_depth_(recv_depth) {
         qpn_ = fabric_->next_qpn.fetch_add(1);
         std::lock_guard<std::mutex> lock(g_qp_registry_mutex);
-        g_qp_registry[qpn_] = this;
+        qp_registry()[qpn_] = this;
     }
     ~LoopbackQp() override {
         std::lock_guard<std::mutex> lock(g_qp_registry_mutex);
-        g_qp_registry.erase(qpn_);
+        qp_registry().erase(qpn_);
     }
 
     void post_send(std::uint64_t wr_id, const Sge& sge, bool signaled, bool) override {
@@ -131,8 +135,8 @@ private:
 
     LoopbackQp* peer_qp() const {
         std::lock_guard<std::mutex> lock(g_qp_registry_mutex);
-        auto it = g_qp_registry.find(peer_qpn_);
-        return it == g_qp_registry.end() ? nullptr : it->second;
+        auto it = qp_registry().find(peer_qpn_);
+        return it == qp_registry().end() ? nullptr : it->second;
     }
 
     // Executes queued sends in order against `peer` (caller holds the fabric mutex).
