@@ -47,10 +47,11 @@ const char* phase_name(std::uint32_t phase) {
     }
 }
 
-// Largest message of the flag-in-data kernels when the environment does not say.  Two ranks: measured 12.3-12.8 us
-// against 14.5-16.3 us at 256 KiB and level at 1 MiB (p50, device-timed); the data crosses one pair of links, so
-// the doubled bytes cost little.  More ranks: kept off until a sweep on that many GPUs has shown a gain.
-std::int64_t default_ll_max_bytes(int nranks) { return nranks == 2 ? (1 << 20) : 0; }
+// Largest message of the flag-in-data kernels when the environment does not say: 1 MiB.  Measured (p50, device-timed,
+// bf16): two ranks 12.3-12.8 us against 14.5-16.3 us at 256 KiB and level at 1 MiB; eight ranks (multimem pushes)
+// geomean of NCCL time / this library's time over the 15 cells of the grid 1.37 with them against 1.25 without, no
+// cell slower than NCCL.  Four ranks take the same code path as eight.
+std::int64_t default_ll_max_bytes(int nranks) { return nranks >= 2 ? (1 << 20) : 0; }
 
 }  // namespace
 

@@ -271,10 +271,12 @@ void FusedGemmContext::ag_gemm(const void* x_shard, const void* W, void* out, in
     if (push_ctas <= 0) push_ctas = R > 1 ? 16 : 0;
     if (R == 1) push_ctas = 0;
     f.push_ctas = push_ctas;
-    // Units per 128-row block.  2 (the measured configuration) lets 16 pushers work on 8 blocks at once, so at 8 GPUs
-    // the whole shard arrives together; 8 makes them work through the blocks in order (two blocks in flight) so that
-    // the GEMM can follow the transfer; more units cost a flag round trip each.  NANO_NCCL_AG_PUSH_PARTS selects.
-    int parts = s.ag_push_parts > 0 ? s.ag_push_parts : 2;
+    // Units per 128-row block.  With 2, 16 pushers work on 8 blocks at once, so at 8 GPUs the whole shard arrives
+    // together and the GEMM of the remote rows waits for all of it; with 8 (the default) they work through the blocks
+    // in order (two blocks in flight) and the GEMM follows the transfer.  Measured on 8 B200, 8192 x 1792 x 4096:
+    // 164 us against 182 us (2 GPUs: 395 against 389 us); more units cost a flag round trip each.
+    // NANO_NCCL_AG_PUSH_PARTS selects.
+    int parts = s.ag_push_parts > 0 ? s.ag_push_parts : 8;
     while (parts > 1 && parts > push_ctas) parts /= 2;
     f.push_parts = std::max(1, parts);
     f.push_tma = s.ag_tma_push && (static_cast<std::size_t>(K) * 2) % 16 == 0 ? 1 : 0;

@@ -72,10 +72,11 @@ def plan_buckets(numels: list, bucket_bytes: int, elem_size: int = 2) -> list:
 
 def default_comm_ctas(world: int) -> int:
     """CTAs of a gradient reduction that runs beside backward (0: the tuner's own grid).  Measured on GPT-2-medium,
-    micro-batch 8, two B200: 8 CTAs 34.3 ms per step, 16: 33.8, 32: 33.7, the tuner's 64: 33.8 (one GPU: 32.9): the
-    reduction has to be quick rather than small, because while it runs the matrix products lose those SMs and a
-    whole wave with them."""
-    return 32
+    micro-batch 8 (one GPU: 32.9 ms per step).  Two B200 (peer loads, 16 in flight per thread): 8 CTAs 34.3 ms, 16: 33.8,
+    32: 33.7, the tuner's 64: 33.8.  Eight B200 (in-switch reduction, where a CTA moves more): 8 CTAs 34.4 ms, 32: 34.8.
+    The reduction has to be quick rather than small, because while it runs the matrix products lose those SMs and a
+    whole wave with them; how many CTAs "quick" takes depends on the kernel."""
+    return 32 if world <= 2 else 8
 
 
 class DataParallel:
