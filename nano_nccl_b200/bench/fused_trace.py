@@ -7,7 +7,9 @@ kernel's diagnostic time line switched on and prints, for this rank, a digest ov
   * drain        accumulator complete -> handed back (tag 1 -> tag 3): large means the epilogue (its remote
                  stores) is the bottleneck;
   * peer wait    own tiles: accumulator complete -> partials arrived (tag 1 -> tag 2);
-  * block wait   AllGather->GEMM producer waiting for a remote row block (tag 5 -> tag 6).
+  * block wait   AllGather->GEMM producer waiting for a remote row block (tag 5 -> tag 6);
+  * publish      GEMM->ReduceScatter flag publisher inside the release store of a foreign tile's flag
+                 (tag 7 -> tag 4): the wait for that tile's remote stores to be acknowledged.
 
     NANO_NCCL_GEMM_TRACE=1 torchrun --nproc-per-node 8 -m nano_nccl_b200.bench.fused_trace [--op gemm_rs|ag_gemm]
 
@@ -30,7 +32,7 @@ from nano_nccl_b200.ops.gemm import FusedTensorParallel
 def digest(trace: dict) -> dict:
     first = min(ev[0][1] for roles in trace.values() for ev in roles.values())
     last = max(ev[-1][1] for roles in trace.values() for ev in roles.values())
-    mma_wait, drain, peer_wait, block_wait, tiles = [], [], [], [], []
+    mma_wait, drain, peer_wait, block_wait, publish, tiles = [], [], [], [], [], []
     for roles in trace.values():
         ep = roles.get("epilogue", [])
         w = d = pw = 0
@@ -56,18 +58,21 @@ def digest(trace: dict) -> dict:
             peer_wait.append(pw)
             tiles.append(ntiles)
         pr = roles.get("producer", [])
-        bw, start = 0, None
+        bw, pb, start = 0, 0, None
         for tag, t in pr:
-            if tag == 5:
+            if tag in (5, 7):
                 start = t
             elif tag == 6 and start is not None:
                 bw += t - start
+            elif tag == 4 and start is not None:
+                pb += t - start
         if pr:
             block_wait.append(bw)
+            publish.append(pb)
     med = lambda xs: statistics.median(xs) / 1e3 if xs else 0.0  # noqa: E731
     return {"ctas": len(trace), "span_us": (last - first) / 1e3, "tiles_per_cta": statistics.median(tiles) if tiles else 0,
             "mma_wait_us": med(mma_wait), "drain_us": med(drain), "peer_wait_us": med(peer_wait),
-            "block_wait_us": med(block_wait), "block_wait_max_us": max(block_wait) / 1e3 if block_wait else 0.0}
+            "publish_us": med(publish), "block_wait_us": med(block_wait), "block_wait_max_us": max(block_wait) / 1e3 if block_wait else 0.0}
 
 
 def main() -> None:

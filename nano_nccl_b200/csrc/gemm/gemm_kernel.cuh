@@ -35,8 +35,9 @@ constexpr int kBM = 128, kBN = 256, kBK = 64;
 constexpr int kStages = 4;
 constexpr int kAccStages = 2;
 constexpr int kTmemCols = 512;
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 224;      // warp 0 TMA, 1 MMA, 2..5 epilogue, 6 publishes the tile flags of GemmRs
 constexpr int kEpilogueThreads = 128;
+constexpr int kPublisherWarp = 6;
 constexpr std::uint32_t kStageBytesA = kBM * kBK * 2;
 constexpr std::uint32_t kStageBytesB = kBN * kBK * 2;
 constexpr std::uint32_t kStageBytes = kStageBytesA + kStageBytesB;
@@ -48,7 +49,7 @@ constexpr std::uint32_t kTmaBoxBytes = 32 * 128;                // one 64-column
 constexpr int kMaxPushParts = 32;                               // AgGemm: most push units a 128-row block is cut into
 constexpr std::size_t kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget of one CTA");
-static_assert((2 * kStages + 2 * kAccStages + 1) * 8 + 8 <= 256, "barrier area");
+static_assert((2 * kStages + 2 * kAccStages + 1) * 8 + 12 <= 256, "barrier area");
 
 // GemmRsTma is GemmRs with the remote part of the epilogue done by the TMA unit: a foreign tile is
 // staged in shared memory in the 128-byte-swizzle layout and written into the owner's staging with
@@ -94,9 +95,10 @@ struct FusedArgs {
     // the blocks as they arrive instead of waiting for the whole shard.
     int push_parts = 2;
     // Diagnostic time line (null: off).  kTraceSlots words per CTA and role: role 0 = the epilogue's first
-    // thread, role 1 = the TMA producer.  A word is (tag << 60) | %globaltimer: tag 0 kernel entry,
-    // 1 accumulator complete, 2 the peers' partials have arrived (own tiles), 3 accumulator handed back,
-    // 4 tile flag published, 5 / 6 producer starts / ends waiting for a remote row block.
+    // thread, role 1 = the TMA producer (AgGemm) or the flag publisher (GemmRs).  A word is
+    // (tag << 60) | %globaltimer: tag 0 kernel entry, 1 accumulator complete, 2 the peers' partials have
+    // arrived (own tiles), 3 accumulator handed back, 7 all four warps have issued a foreign tile's stores,
+    // 4 that tile's flag published, 5 / 6 producer starts / ends waiting for a remote row block.
     unsigned long long* trace = nullptr;
     unsigned long long timeout_ns = 0;
 };
@@ -186,9 +188,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     std::uint64_t* empty_bar = bars + kStages;               // [kStages]
     std::uint64_t* acc_full = bars + 2 * kStages;            // [kAccStages]
     std::uint64_t* acc_empty = bars + 2 * kStages + kAccStages;  // [kAccStages]
-    std::uint64_t* epi_bar = bars + 2 * kStages + 2 * kAccStages;  // epilogue warps -> flag writer
+    std::uint64_t* epi_bar = bars + 2 * kStages + 2 * kAccStages;  // epilogue warps -> flag publisher
     std::uint32_t* tmem_slot = reinterpret_cast<std::uint32_t*>(bars + 2 * kStages + 2 * kAccStages + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    // phases of epi_bar the publisher has seen complete; an epilogue warp arrives for its j-th foreign tile
+    // only once this is >= j, so an arrival can never count toward an earlier tile's phase
+    volatile std::uint32_t* epi_seen = reinterpret_cast<volatile std::uint32_t*>(tmem_slot + 2);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -288,6 +293,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         mbar_init(epi_bar, kEpilogueThreads / 32);
         *abort_flag = 0;
+        *epi_seen = 0;
         fence_barrier_init();
         prefetch_tensormap(&tmap_a);
         prefetch_tensormap(&tmap_b);
@@ -398,14 +404,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
             }
         }
-    } else {
+    } else if (warp < kPublisherWarp) {
         // ------------------------------------------------------------ epilogue (warps 2..5)
         const int quad = warp & 3;                    // TMEM lane quadrant this warp may read
         const int row_in_tile = quad * 32 + lane;
         int acc = 0;
         int epi_slot = 0;
         const bool tracer = threadIdx.x == 64;
-        std::uint32_t acc_phase = 0, epi_phase = 0;
+        std::uint32_t acc_phase = 0, foreign_tiles = 0;
         if (tracer) trace_stamp(f, 0, &epi_slot, 0);
         for (int t = cta; t < total_tiles; t += num_ctas) {
             int tm, tn, owner;
@@ -604,31 +610,75 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (tracer) trace_stamp(f, 0, &epi_slot, 3);
             if constexpr (kIsRs<kMode>) {
                 if (owner != f.rank) {
-                    // The tile's flag follows the stores of all four epilogue warps: each warp
-                    // arrives on epi_bar after its stores; one thread waits (bounded) and then
-                    // publishes the flag with release semantics.  Nobody else waits.
-                    if (kMode == Mode::GemmRsTma && lane == 0) {
-                        // tensor stores are asynchronous: they must have completed, and be ordered before
-                        // ordinary memory operations, before this warp counts as done
-                        bulk_wait_group_all();
-                        fence_proxy_async_all();
-                        __threadfence_system();
-                    }
-                    if (lane == 0) mbar_arrive(epi_bar);
-                    if (threadIdx.x == 64) {
-                        if (mbar_wait(epi_bar, epi_phase)) {
-                            dev::st_release_sys(f.flags[owner] + f.rank * tiles_per_owner + tile_in_owner, f.epoch);
-                            trace_stamp(f, 0, &epi_slot, 4);
-                        } else {
-                            gemm_fail(g, kGemmWaitEpilogue, abort_flag);
+                    // The tile's flag follows the stores of all four epilogue warps: each warp arrives on
+                    // epi_bar after its stores and goes on to the next tile; the publisher warp waits for the
+                    // four arrivals and publishes the flag with release semantics.  The fence that store
+                    // implies waits for every remote store of the tile to be acknowledged (microseconds over
+                    // NVLink), which is why no epilogue warp executes it.
+                    bool ok = true;
+                    if (lane == 0) {
+                        if (kMode == Mode::GemmRsTma) {
+                            // tensor stores are asynchronous: they must have completed, and be ordered before
+                            // ordinary memory operations, before this warp counts as done
+                            bulk_wait_group_all();
+                            fence_proxy_async_all();
+                            __threadfence_system();
                         }
+                        const unsigned long long start = dev::global_timer_ns();
+                        unsigned spins = 0;
+                        while (*epi_seen < foreign_tiles) {
+                            if ((++spins & 63u) == 0u &&
+                                (*abort_flag != 0 || dev::global_timer_ns() - start > f.timeout_ns)) {
+                                ok = false;
+                                break;
+                            }
+                        }
+                        if (ok) mbar_arrive(epi_bar);
                     }
-                    epi_phase ^= 1u;
+                    ++foreign_tiles;
+                    if (!__all_sync(0xffffffffu, ok)) {
+                        gemm_fail(g, kGemmWaitEpilogue, abort_flag);
+                        break;
+                    }
                 }
             }
             if (++acc == kAccStages) {
                 acc = 0;
                 acc_phase ^= 1u;
+            }
+        }
+    } else if (warp == kPublisherWarp) {
+        // ------------------------------------------------------------ GemmRs: tile-flag publisher
+        if constexpr (kIsRs<kMode>) {
+            if (lane == 0) {
+                const int tiles_per_owner = (m_tiles / f.nranks) * n_tiles;
+                int pub_slot = 0;
+                std::uint32_t phase = 0, seen = 0;
+                for (int t = cta; t < total_tiles; t += num_ctas) {
+                    int tm, tn, owner;
+                    tile_coords<kMode>(t, m_tiles, n_tiles, f, &tm, &tn, &owner);
+                    if (owner == f.rank) continue;
+                    const unsigned long long start = dev::global_timer_ns();
+                    unsigned spins = 0;
+                    bool ok = true;
+                    while (!mbar_try_wait(epi_bar, phase)) {
+                        if ((++spins & 63u) == 0u &&
+                            (*abort_flag != 0 || dev::global_timer_ns() - start > f.timeout_ns)) {
+                            ok = false;
+                            break;
+                        }
+                    }
+                    if (!ok) {
+                        if (*abort_flag == 0) gemm_fail(g, kGemmWaitEpilogue, abort_flag);
+                        break;
+                    }
+                    *epi_seen = ++seen;
+                    phase ^= 1u;
+                    trace_stamp(f, 1, &pub_slot, 7);
+                    const int tile_in_owner = (tm - owner * (m_tiles / f.nranks)) * n_tiles + tn;
+                    dev::st_release_sys(f.flags[owner] + f.rank * tiles_per_owner + tile_in_owner, f.epoch);
+                    trace_stamp(f, 1, &pub_slot, 4);
+                }
             }
         }
     }

@@ -75,7 +75,8 @@ class FusedTensorParallel:
         """Time line of the last fused call as {cta: {"epilogue": [(tag, ns), ...], "producer": [...]}}; needs
         NANO_NCCL_GEMM_TRACE=1 in the environment when this object was created (empty dict otherwise).
         Tags: 0 kernel entry, 1 accumulator complete, 2 peers' partials arrived, 3 accumulator handed back,
-        4 tile flag published, 5 / 6 producer starts / ends waiting for a remote row block."""
+        5 / 6 producer starts / ends waiting for a remote row block (AllGather->GEMM); in GEMM->ReduceScatter the
+        "producer" list is the flag publisher's: 7 a foreign tile's stores all issued, 4 its flag published."""
         cap = (256 + 64) * 2 * 128
         buf = (C.c_ulonglong * cap)()
         n = C.c_size_t(0)

@@ -41,8 +41,13 @@ def run_ranks(worker: str, nranks: int, args: list[str] | None = None, env: dict
     port = free_port()
     master_port = free_port()
     procs = []
+    # the ranks compute reference results on the CPU at the same time: share the cores instead of letting
+    # every rank start one thread per core
+    threads = str(max(1, min(8, (os.cpu_count() or 8) // max(nranks, 1))))
     for r in range(nranks):
         e = dict(os.environ)
+        e.setdefault("OMP_NUM_THREADS", threads)
+        e.setdefault("MKL_NUM_THREADS", threads)
         e.update({"RANK": str(r), "WORLD_SIZE": str(nranks), "LOCAL_RANK": str(r),
                   "NANO_TEST_PORT": str(port), "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(master_port),
                   "PYTHONPATH": str(ROOT) + os.pathsep + e.get("PYTHONPATH", "")})

@@ -33,3 +33,16 @@ def gpu_count() -> int:
         return torch.cuda.device_count() if torch.cuda.is_available() else 0
     except Exception:
         return 0
+
+
+def multi_gpu_ranks(most: int = 8) -> int:
+    """Rank count of a multi-GPU test: 2 by default, or the largest of 2 / 4 / 8 that fits the visible GPUs,
+    `most` and NANO_NCCL_TEST_RANKS when that variable is set (one process per GPU).  Skips below 2 GPUs.
+    The default stays at 2 because the host side of a test (reference results on the CPU, one interpreter per
+    rank) grows with the rank count and a whole-suite run at 8 ranks takes many times longer."""
+    n = gpu_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    want = int(os.environ.get("NANO_NCCL_TEST_RANKS", "2"))
+    cap = min(n, most, max(want, 2))
+    return 8 if cap >= 8 else 4 if cap >= 4 else 2

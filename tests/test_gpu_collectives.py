@@ -2,16 +2,13 @@
 import pytest
 
 from _spawn import run_ranks
-from conftest import gpu_count
+from conftest import multi_gpu_ranks
 
 pytestmark = pytest.mark.gpu
 
 
 def _ranks():
-    n = gpu_count()
-    if n < 2:
-        pytest.skip("needs at least 2 GPUs")
-    return 8 if n >= 8 else 4 if n >= 4 else 2
+    return multi_gpu_ranks()
 
 
 @pytest.mark.parametrize("mode", ["matrix", "nan", "invalid", "symmetric", "large", "symmetric_rs_ag", "symmetric_pool",

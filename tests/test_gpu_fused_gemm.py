@@ -2,7 +2,7 @@
 import pytest
 
 from _spawn import run_ranks
-from conftest import gpu_count
+from conftest import multi_gpu_ranks
 
 pytestmark = pytest.mark.gpu
 
@@ -13,9 +13,6 @@ VARIANTS = [{}, {"NANO_NCCL_GEMM_RS_TMA": "1"}, {"NANO_NCCL_AG_GEMM_TMA": "1"}, 
 
 @pytest.mark.parametrize("env", VARIANTS, ids=lambda e: ",".join(f"{k}={v}" for k, v in e.items()) or "default")
 def test_fused_gemm_collectives(env):
-    n = gpu_count()
-    if n < 2:
-        pytest.skip("needs at least 2 GPUs")
-    ranks = 8 if n >= 8 else 4 if n >= 4 else 2
+    ranks = multi_gpu_ranks()
     outs = run_ranks("fused_gemm_worker.py", ranks, env=env, timeout=600)
     assert all("fused ok" in o for o in outs), outs

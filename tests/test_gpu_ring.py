@@ -2,20 +2,17 @@
 import pytest
 
 from _spawn import run_ranks
-from conftest import gpu_count
+from conftest import multi_gpu_ranks
 
 pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("transport", ["p2p", "shm", "socket"])
 def test_ring_fallback(transport):
-    n = gpu_count()
-    if n < 2:
-        pytest.skip("needs at least 2 GPUs")
+    ranks = multi_gpu_ranks(4)
     env = {}
     if transport == "socket":
         # no network on the test machines: the loopback interface stands in for the NIC
         env = {"NANO_NCCL_SOCKET_IFNAME": "lo", "NANO_NCCL_SOCKET_ALLOW_LOOPBACK": "1"}
-    ranks = 4 if n >= 4 else 2
     outs = run_ranks("ring_worker.py", ranks, [transport], env=env, timeout=600)
     assert all(f"ring {transport} ok" in o for o in outs), outs

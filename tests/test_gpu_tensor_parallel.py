@@ -3,15 +3,12 @@ NCCL collectives, forward and backward, 2+ GPUs."""
 import pytest
 
 from _spawn import run_ranks
-from conftest import gpu_count
+from conftest import multi_gpu_ranks
 
 pytestmark = pytest.mark.gpu
 
 
 def test_sequence_parallel_block_on_fused_kernels():
-    n = gpu_count()
-    if n < 2:
-        pytest.skip("needs at least 2 GPUs")
-    ranks = 8 if n >= 8 else 4 if n >= 4 else 2
+    ranks = multi_gpu_ranks()
     outs = run_ranks("tp_gpu_worker.py", ranks, timeout=300)
     assert all("tp gpu ok" in o for o in outs), outs
