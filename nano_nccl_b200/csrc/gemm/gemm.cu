@@ -154,6 +154,7 @@ struct FusedGemmContext::State {
     RawDeviceBuffer trace;       // NANO_NCCL_GEMM_TRACE=1: per-CTA time line of the last fused call
     std::size_t trace_words = 0;
     int ag_push_parts = 0;       // NANO_NCCL_AG_PUSH_PARTS: units per 128-row block (power of two, 1..32); 0 = default
+    int ag_push_ctas = 0;        // NANO_NCCL_AG_PUSH_CTAS: CTAs that only move data in AllGather->GEMM; 0 = default
     bool ag_tma_push = false;    // NANO_NCCL_AG_GEMM_TMA=1: AllGather->GEMM pushers use TMA bulk copies
     bool rs_tma_stores = false;  // NANO_NCCL_GEMM_RS_TMA=1: remote epilogue through TMA tensor stores
 };
@@ -176,6 +177,7 @@ FusedGemmContext::FusedGemmContext(Communicator& comm, std::size_t max_rs_bytes,
     s_->rs_tma_stores = env::flag("NANO_NCCL_GEMM_RS_TMA", false);
     s_->ag_tma_push = env::flag("NANO_NCCL_AG_GEMM_TMA", false);
     s_->ag_push_parts = static_cast<int>(env::integer("NANO_NCCL_AG_PUSH_PARTS", 0, 0, kMaxPushParts));
+    s_->ag_push_ctas = static_cast<int>(env::integer("NANO_NCCL_AG_PUSH_CTAS", 0, 0, 64));
     NANO_REQUIRE_ARG((s_->ag_push_parts & (s_->ag_push_parts - 1)) == 0, "NANO_NCCL_AG_PUSH_PARTS must be a power of two");
     if (env::flag("NANO_NCCL_GEMM_TRACE", false)) {
         int sms = 0;
@@ -268,7 +270,11 @@ void FusedGemmContext::ag_gemm(const void* x_shard, const void* W, void* out, in
     }
     f.gathered_mc = static_cast<__nv_bfloat16*>(comm_.multicast_pointer(s.ag_gathered[parity]));
     f.shard = static_cast<const __nv_bfloat16*>(x_shard);
-    if (push_ctas <= 0) push_ctas = R > 1 ? 16 : 0;
+    // Pushers take SMs from the GEMM for the whole kernel, so as few as keep the transfer ahead of the MMAs: with 2
+    // ranks the own half of the rows (half of the GEMM) is computed before the first remote block is needed and only
+    // one peer is written, so 8 are enough; from 4 ranks on 16.  NANO_NCCL_AG_PUSH_CTAS overrides.
+    if (push_ctas <= 0) push_ctas = s.ag_push_ctas > 0 ? s.ag_push_ctas : (R == 2 ? 8 : 16);
+    push_ctas = std::min(push_ctas, std::max(1, st.sms / 2));
     if (R == 1) push_ctas = 0;
     f.push_ctas = push_ctas;
     // Units per 128-row block.  With 2, 16 pushers work on 8 blocks at once, so at 8 GPUs the whole shard arrives

@@ -104,3 +104,50 @@ def test_clock_sampler_summary():
     s2 = ClockSampler()
     s2.lines = ["0, 1200, 1965, 300, 0x8, Active, Not Active, Active, Not Active"]
     assert s2.stop()["reasons"] == ["hw_slowdown", "sw_thermal_slowdown"]
+
+
+def test_trace_digest_times_the_flag_publisher_of_gemm_rs():
+    """In GEMM->ReduceScatter the second time line of a CTA belongs to the flag publisher: tag 7 = a foreign
+    tile's stores all issued, tag 4 = its flag published."""
+    trace = {0: {"epilogue": [(0, 1000), (1, 5000), (3, 9000), (1, 12000), (3, 16000)],
+                 "producer": [(7, 9100), (4, 12100), (7, 16200), (4, 18200)]}}
+    d = digest(trace)
+    assert d["publish_us"] == 5.0 and d["block_wait_us"] == 0.0
+    assert d["span_us"] == 17.2
+
+
+def test_headline_grid_summary_and_native_rows():
+    from nano_nccl_b200.bench.headline import busbw_factor, parse_nano_bench, summarize
+
+    assert busbw_factor("all_reduce", 8) == 2 * 7 / 8 and busbw_factor("all_gather", 2) == 0.5
+
+    def cell(impl, coll, nbytes, us, bw):
+        return {"collective": coll, "dtype": "bf16", "bytes": nbytes, "impl": impl, "p50_us": us, "busbw_gbs": bw}
+
+    s = summarize([cell("nano", "all_reduce", 1 << 20, 10.0, 100.0), cell("nccl", "all_reduce", 1 << 20, 20.0, 50.0),
+                   cell("nano", "all_gather", 1 << 20, 30.0, 40.0), cell("nccl", "all_gather", 1 << 20, 15.0, 80.0)])
+    assert s["cells_compared"] == 2 and s["cells_faster_than_nccl"] == 1
+    assert s["geomean_nccl_time_over_nano_time"] == 1.0          # 2.0 and 0.5
+    assert s["cells_slower_than_nccl"] == [{"collective": "all_gather", "dtype": "bf16", "bytes": 1 << 20, "ratio": 0.5}]
+    assert s["geomean_busbw_gbs"] == round((100.0 * 40.0) ** 0.5, 2)
+    rows = parse_nano_bench("\n".join([
+        "# header",
+        "collective     dtype op   algo          bytes        count    host_us  dev_p50us  dev_avgus     algbw     busbw  wrong  max_abs",
+        "all_reduce     float sum  oneshot       262144        65536      27.81      19.94      19.88     13.15     13.15      0        0",
+    ]))
+    assert rows == [{"collective": "all_reduce", "dtype": "float", "bytes": 262144, "algo": "oneshot", "host_us": 27.81,
+                     "dev_p50_us": 19.94, "busbw_gbs": 13.15, "wrong": 0}]
+
+
+def test_multi_gpu_rank_choice(monkeypatch):
+    import conftest
+
+    monkeypatch.setattr(conftest, "gpu_count", lambda: 8)
+    monkeypatch.delenv("NANO_NCCL_TEST_RANKS", raising=False)
+    assert conftest.multi_gpu_ranks() == 2
+    monkeypatch.setenv("NANO_NCCL_TEST_RANKS", "8")
+    assert conftest.multi_gpu_ranks() == 8 and conftest.multi_gpu_ranks(4) == 4
+    monkeypatch.setenv("NANO_NCCL_TEST_RANKS", "4")
+    assert conftest.multi_gpu_ranks() == 4
+    monkeypatch.setattr(conftest, "gpu_count", lambda: 3)
+    assert conftest.multi_gpu_ranks() == 2
