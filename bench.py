@@ -52,6 +52,8 @@ def parse_args():
     ap.add_argument("--comm-ctas", type=int, default=-1, help="CTAs of a gradient reduction beside backward (-1: the engine's default, 0: the tuner's grid)")
     ap.add_argument("--shard-optimizer", action="store_true",
                     help="optimizer-state sharding: ReduceScatter + AdamW on 1/N + AllGather instead of AllReduce + AdamW")
+    ap.add_argument("--extras-deadline-s", type=float, default=420.0,
+                    help="every rank exits (0) this long after the timed steps if the extra measurements are stuck")
     ap.add_argument("--no-tail-full-grid", action="store_true",
                     help="keep the few-CTA grid also for the last gradient bucket (nothing overlaps with it)")
     ap.add_argument("--nano-linear", action="store_true", help="forward GEMMs of the linear layers on the tcgen05 kernel")
@@ -242,33 +244,12 @@ def main() -> None:
 
     dev_ms = reduce_max(dev_ms)
     e2e_ms = reduce_max(e2e_ms)
-    breakdown = None
-    if args.impl == "nano":   # three more steps with events around every bucket's reduction (not timed above)
-        engine.enable_timeline(True)
-        for i in range(3):
-            train_step(dev_idx[i % pool], dev_tgt[i % pool])
-        breakdown = engine.timeline_summary()
-        engine.enable_timeline(False)
-    collectives = None
-    if world > 1 and args.impl == "nano" and not args.no_collectives:
-        from nano_nccl_b200.bench.headline import collective_grid
-
-        comm.set_grid_override(0)
-        collectives = collective_grid(comm, world)
-    if comm is not None:
-        comm.destroy()
-        comm = None
-    if world > 1:
-        dist.destroy_process_group()
+    out = None
     if rank == 0:
-        if collectives is not None and not args.no_native_table:
-            from nano_nccl_b200.bench.headline import native_table
-
-            collectives["native_table"] = native_table(world)
-        value = tokens_per_step * args.steps / (dev_ms / 1e3)
-        e2e_value = tokens_per_step * args.steps / (e2e_ms / 1e3)
         from nano_nccl_b200 import _native
 
+        value = tokens_per_step * args.steps / (dev_ms / 1e3)
+        e2e_value = tokens_per_step * args.steps / (e2e_ms / 1e3)
         out = {
             "metric": METRIC_TRAIN,
             "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
@@ -285,12 +266,64 @@ def main() -> None:
             "clocks": clocks, "final_loss": round(final_loss, 4),
             "native_library": _native.library_loaded_path(),
         }
-        if breakdown is not None:
-            out["step_breakdown"] = breakdown
-        if collectives is not None:
-            out["collectives"] = collectives
-            out["gpu_launches_collective_grid"] = collectives["nano_kernel_launches"]
-        print(json.dumps(out), flush=True)
+
+    # Everything below adds detail to the line and is not part of the timed measurement.  It must never cost the
+    # line itself: an error is recorded in the line, and a deadline ends every rank (exit 0, rank 0 prints what it
+    # has) if a rank is stuck in a collective that its peers have left.
+    import threading
+
+    printed = threading.Event()
+
+    def emit(note: str | None = None) -> None:
+        if rank == 0 and not printed.is_set():
+            printed.set()
+            if note is not None:
+                out.setdefault("notes", []).append(note)
+            print(json.dumps(out), flush=True)
+
+    def deadline_passed() -> None:
+        emit(f"the measurements after the timed steps did not finish within {args.extras_deadline_s} s")
+        os._exit(0)
+
+    watchdog = threading.Timer(args.extras_deadline_s, deadline_passed)
+    watchdog.daemon = True
+    watchdog.start()
+    collectives = None
+    try:
+        if args.impl == "nano":   # three more steps with events around every bucket's reduction (not timed above)
+            engine.enable_timeline(True)
+            for i in range(3):
+                train_step(dev_idx[i % pool], dev_tgt[i % pool])
+            breakdown = engine.timeline_summary()
+            engine.enable_timeline(False)
+            if out is not None:
+                out["step_breakdown"] = breakdown
+        if world > 1 and args.impl == "nano" and not args.no_collectives:
+            from nano_nccl_b200.bench.headline import collective_grid
+
+            comm.set_grid_override(0)
+            collectives = collective_grid(comm, world)
+            if out is not None:
+                out["collectives"] = collectives
+                out["gpu_launches_collective_grid"] = collectives["nano_kernel_launches"]
+        if comm is not None:
+            comm.destroy()
+            comm = None
+        if world > 1:
+            dist.destroy_process_group()
+    except Exception as e:  # noqa: BLE001 - the line is printed with the error in it; peers leave at the deadline
+        emit(f"after the timed steps: {type(e).__name__}: {str(e)[:300]}")
+        os._exit(0)
+    watchdog.cancel()
+    if rank == 0:
+        if collectives is not None and not args.no_native_table:
+            from nano_nccl_b200.bench.headline import native_table
+
+            try:
+                collectives["native_table"] = native_table(world)
+            except Exception as e:  # noqa: BLE001
+                collectives["native_table"] = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
+        emit()
 
 
 if __name__ == "__main__":

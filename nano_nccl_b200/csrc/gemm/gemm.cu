@@ -113,6 +113,24 @@ int gemm_pick_tile_width(int m_tiles, int N, int ctas, int granule) {
     return best;
 }
 
+GemmTailSplit gemm_pick_tail_split(int tiles, int ctas, int bn) {
+    GemmTailSplit none;
+    none.first_tile = tiles;
+    if (!env::flag("NANO_NCCL_GEMM_TAIL", true) || ctas <= 0 || tiles <= ctas) return none;
+    const int rest = tiles % ctas;
+    if (rest == 0 || rest * 2 > ctas) return none;
+    for (int piece = 32; piece <= 128; piece *= 2) {
+        if (bn % piece != 0 || piece >= bn) continue;
+        if (static_cast<long>(rest) * (bn / piece) <= ctas) {
+            GemmTailSplit split;
+            split.first_tile = tiles - rest;
+            split.piece_bn = piece;
+            return split;
+        }
+    }
+    return none;
+}
+
 void gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, cudaStream_t stream,
                int max_ctas) {
     NANO_REQUIRE_ARG(A != nullptr && B != nullptr && C != nullptr, "GEMM operands must be non-null");
@@ -133,7 +151,12 @@ void gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, i
     const int tiles = ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
     int grid = max_ctas > 0 ? std::min(max_ctas, st.sms) : st.sms;
     grid = std::max(1, std::min(grid, tiles));
-    gemm_bf16_kernel<Mode::Plain><<<grid, kGemmThreads, kSmemBytes, stream>>>(ta, tb, ta, g, f, PeerMaps{});
+    // the last, partly filled round of tiles is cut into narrow column pieces (their own tensor map of B)
+    const GemmTailSplit tail = gemm_pick_tail_split(tiles, grid, bn);
+    g.tail_first = tail.first_tile;
+    g.tail_bn = tail.piece_bn;
+    const CUtensorMap tb_tail = tail.piece_bn > 0 ? make_tmap(B, N, K, tail.piece_bn) : tb;
+    gemm_bf16_kernel<Mode::Plain><<<grid, kGemmThreads, kSmemBytes, stream>>>(ta, tb, tb_tail, g, f, PeerMaps{});
     CUDA_CHECK_THROW(cudaGetLastError());
 }
 

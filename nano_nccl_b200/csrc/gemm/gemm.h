@@ -26,6 +26,18 @@ void gemm_clear_error(int device);
 // whole waves of CTAs times the width, ties to the wider tile.  Throws std::invalid_argument on a bad setting.
 int gemm_pick_tile_width(int m_tiles, int N, int ctas, int granule = 32);
 
+// Split of the last, partly filled wave of a persistent GEMM.  `tiles` output tiles of `bn` columns walked by
+// `ctas` CTAs leave tiles % ctas tiles for a last round in which most CTAs idle; when that remainder is at most
+// half the CTAs, its tiles are cut into column pieces of `piece_bn` (128, 64 or 32: the narrowest width whose
+// pieces still fit one round) so that the round costs a fraction of a full tile instead of a whole one.
+// Returns {first linear tile index of the split part, piece_bn}; piece_bn == 0: no split.
+// NANO_NCCL_GEMM_TAIL=0 switches the split off.
+struct GemmTailSplit {
+    int first_tile = 0;
+    int piece_bn = 0;
+};
+GemmTailSplit gemm_pick_tail_split(int tiles, int ctas, int bn);
+
 // Workspace and flags of the fused kernels for one (M, N, K) problem family on one communicator.
 // Collective to construct (symmetric allocations).
 class FusedGemmContext {

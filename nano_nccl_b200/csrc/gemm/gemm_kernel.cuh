@@ -112,6 +112,11 @@ struct GemmArgs {
     // Columns per tile: kBN, or a smaller multiple of 32 (of 64 with tensor stores) chosen by the host so
     // that the tile count fills whole waves of CTAs; shared memory and TMEM are laid out for kBN either way.
     int bn = kBN;
+    // Plain mode: linear tile indices >= tail_first (the last, partly filled round of the persistent walk) are cut
+    // into bn / tail_bn column pieces of tail_bn columns each, loaded through a tensor map of B whose box is that
+    // narrow; tail_bn == 0: no split.
+    int tail_first = 0;
+    int tail_bn = 0;
 };
 
 constexpr int kTraceSlots = 128;
@@ -172,10 +177,39 @@ __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, con
     }
 }
 
+// One item of a CTA's walk: an output tile, or in Plain mode a column piece of a tile of the last round.
+struct TileWork {
+    int tm, tn, owner;
+    int col0;   // first output column
+    int bn;     // columns computed
+    bool tail;  // a piece: B comes through the narrow tensor map
+};
+
+template <Mode kMode>
+__device__ __forceinline__ TileWork tile_work(int t, int m_tiles, int n_tiles, const GemmArgs& g, const FusedArgs& f) {
+    TileWork w;
+    w.bn = g.bn;
+    w.tail = false;
+    int lin = t, col_off = 0;
+    if constexpr (kMode == Mode::Plain) {
+        if (g.tail_bn > 0 && t >= g.tail_first) {
+            const int pieces = g.bn / g.tail_bn;
+            const int p = t - g.tail_first;
+            lin = g.tail_first + p / pieces;
+            col_off = (p % pieces) * g.tail_bn;
+            w.bn = g.tail_bn;
+            w.tail = true;
+        }
+    }
+    tile_coords<kMode>(lin, m_tiles, n_tiles, f, &w.tm, &w.tn, &w.owner);
+    w.col0 = w.tn * g.bn + col_off;
+    return w;
+}
+
 template <Mode kMode>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_shard, GemmArgs g, FusedArgs f,
+                 const __grid_constant__ CUtensorMap tmap_aux, GemmArgs g, FusedArgs f,
                  const __grid_constant__ PeerMaps peer_maps) {
     extern __shared__ unsigned char smem_raw[];
     // 1024-byte alignment: required by the 128-byte swizzle atom (8 rows x 128 B)
@@ -200,7 +234,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int m_tiles = (g.M + kBM - 1) / kBM;
     const int n_tiles = (g.N + g.bn - 1) / g.bn;
     const int k_blocks = (g.K + kBK - 1) / kBK;
-    const int total_tiles = m_tiles * n_tiles;
+    // tmap_aux: AgGemm: this rank's un-gathered shard; Plain: B with the narrow box of the tail pieces
+    int total_tiles = m_tiles * n_tiles;
+    if constexpr (kMode == Mode::Plain) {
+        if (g.tail_bn > 0) total_tiles = g.tail_first + (total_tiles - g.tail_first) * (g.bn / g.tail_bn);
+    }
 
     int first_cta = 0, num_ctas = static_cast<int>(gridDim.x);
     if constexpr (kMode == Mode::AgGemm) {
@@ -312,8 +350,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             int producer_slot = 0;
             std::uint32_t phase = 0;
             for (int t = cta; t < total_tiles && *abort_flag == 0; t += num_ctas) {
-                int tm, tn, owner;
-                tile_coords<kMode>(t, m_tiles, n_tiles, f, &tm, &tn, &owner);
+                const TileWork w = tile_work<kMode>(t, m_tiles, n_tiles, g, f);
+                const int tm = w.tm, owner = w.owner;
                 if constexpr (kMode == Mode::AgGemm) {
                     if (owner != f.rank) {
                         // rows of a remote shard: wait until its pusher raised this block's flag
@@ -347,15 +385,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         gemm_fail(g, kGemmWaitProducer, abort_flag);
                         break;
                     }
-                    mbar_arrive_expect_tx(&full_bar[stage], kStageBytesA + static_cast<std::uint32_t>(g.bn) * kBK * 2);
+                    mbar_arrive_expect_tx(&full_bar[stage], kStageBytesA + static_cast<std::uint32_t>(w.bn) * kBK * 2);
                     if (kMode == Mode::AgGemm && owner == f.rank) {
                         // own rows come straight from the un-gathered shard
-                        tma_load_2d(smem_a + stage * kStageBytesA, &tmap_shard, &full_bar[stage], kb * kBK,
+                        tma_load_2d(smem_a + stage * kStageBytesA, &tmap_aux, &full_bar[stage], kb * kBK,
                                     tm * kBM - f.rank * (g.M / f.nranks));
                     } else {
                         tma_load_2d(smem_a + stage * kStageBytesA, &tmap_a, &full_bar[stage], kb * kBK, tm * kBM);
                     }
-                    tma_load_2d(smem_b + stage * kStageBytesB, &tmap_b, &full_bar[stage], kb * kBK, tn * g.bn);
+                    tma_load_2d(smem_b + stage * kStageBytesB, (kMode == Mode::Plain && w.tail) ? &tmap_aux : &tmap_b,
+                                &full_bar[stage], kb * kBK, w.col0);
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1u;
@@ -366,10 +405,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (elect_one()) {
-            const std::uint32_t idesc = make_idesc_bf16(kBM, g.bn);
             int stage = 0, acc = 0;
             std::uint32_t phase = 0, acc_phase = 0;
             for (int t = cta; t < total_tiles && *abort_flag == 0; t += num_ctas) {
+                const std::uint32_t idesc = make_idesc_bf16(kBM, tile_work<kMode>(t, m_tiles, n_tiles, g, f).bn);
                 if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u)) {
                     gemm_fail(g, kGemmWaitMma, abort_flag);
                     break;
@@ -414,8 +453,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         std::uint32_t acc_phase = 0, foreign_tiles = 0;
         if (tracer) trace_stamp(f, 0, &epi_slot, 0);
         for (int t = cta; t < total_tiles; t += num_ctas) {
-            int tm, tn, owner;
-            tile_coords<kMode>(t, m_tiles, n_tiles, f, &tm, &tn, &owner);
+            const TileWork w = tile_work<kMode>(t, m_tiles, n_tiles, g, f);
+            const int tm = w.tm, tn = w.tn, owner = w.owner, bn = w.bn;
             if (*abort_flag != 0) break;
             if (!mbar_wait(&acc_full[acc], acc_phase)) {
                 gemm_fail(g, kGemmWaitEpilogue, abort_flag);
@@ -424,7 +463,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             tcgen05_fence_after_sync();
             if (tracer) trace_stamp(f, 0, &epi_slot, 1);
             const int row = tm * kBM + row_in_tile;
-            const int col0 = tn * g.bn;
+            const int col0 = w.col0;
             bool peer_ok = true;
             __nv_bfloat16* out_row = nullptr;
             int rows_per = 0, tiles_per_owner = 0, tile_in_owner = 0;
@@ -467,14 +506,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const bool row_ok = row < g.M;
             const bool vec_ok = (g.N % 8) == 0 && (reinterpret_cast<std::uintptr_t>(warp_out) & 15u) == 0;
             unsigned char* stage = smem_epi + (warp - 2) * kEpiWarpBytes;
-            const int n_end = col0 + g.bn < g.N ? col0 + g.bn : g.N;  // first column that is not this tile's
+            const int n_end = col0 + bn < g.N ? col0 + bn : g.N;  // first column that is not this tile's
 #pragma unroll 1
             for (int half = 0; half < kBN / kEpiCols; ++half) {
-                if (half * kEpiCols >= g.bn) break;
+                if (half * kEpiCols >= bn) break;
 #pragma unroll 1
                 for (int cc = 0; cc < kEpiCols / 32; ++cc) {
                     const int c = half * (kEpiCols / 32) + cc;
-                    if (c * 32 >= g.bn) break;  // a narrower tile has fewer 32-column chunks
+                    if (c * 32 >= bn) break;  // a narrower tile has fewer 32-column chunks
                     std::uint32_t r[32];
                     const std::uint32_t taddr = tmem_base + (static_cast<std::uint32_t>(quad * 32) << 16) +
                                                 static_cast<std::uint32_t>(acc * kBN + c * 32);

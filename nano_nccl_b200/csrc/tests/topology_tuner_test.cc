@@ -201,6 +201,28 @@ int main() {
         CHECK_THROWS_WITH(gemm_pick_tile_width(64, 1792, 148, 64), "multiple of 64");
         unsetenv("NANO_NCCL_GEMM_BN");
     }
+    {   // split of the last, partly filled round of a persistent GEMM into narrow column pieces
+        unsetenv("NANO_NCCL_GEMM_TAIL");
+        GemmTailSplit t = gemm_pick_tail_split(448, 148, 256);      // 8192 x 1792: 4 tiles left -> 32 pieces of 32 columns
+        CHECK(t.first_tile == 444 && t.piece_bn == 32);
+        t = gemm_pick_tail_split(512, 148, 256);                    // 4096^2: 68 left -> 136 pieces of 128 columns
+        CHECK(t.first_tile == 444 && t.piece_bn == 128);
+        t = gemm_pick_tail_split(462, 148, 256);                    // 18 left: 8 pieces each fit (144), so 32 columns
+        CHECK(t.first_tile == 444 && t.piece_bn == 32);
+        t = gemm_pick_tail_split(474, 148, 256);                    // 30 left: 4 pieces each (120) -> 64 columns
+        CHECK(t.first_tile == 444 && t.piece_bn == 64);
+        t = gemm_pick_tail_split(2048, 148, 256);                   // 124 left: more than half the CTAs, no split
+        CHECK(t.first_tile == 2048 && t.piece_bn == 0);
+        t = gemm_pick_tail_split(1024, 128, 256);                   // whole rounds
+        CHECK(t.piece_bn == 0);
+        t = gemm_pick_tail_split(100, 148, 256);                    // a single round
+        CHECK(t.piece_bn == 0);
+        t = gemm_pick_tail_split(452, 148, 224);                    // 224 columns: only 32 divides it
+        CHECK(t.first_tile == 444 && t.piece_bn == 32);
+        setenv("NANO_NCCL_GEMM_TAIL", "0", 1);
+        CHECK(gemm_pick_tail_split(448, 148, 256).piece_bn == 0);
+        unsetenv("NANO_NCCL_GEMM_TAIL");
+    }
     std::printf("topology_tuner_test ok\n");
     return 0;
 }

@@ -12,8 +12,13 @@ def _ref(a, b, bias=None):
     return out
 
 
+# The second line are shapes whose last round of tiles is cut into column pieces on a 148-SM GPU: 448 tiles (4 left:
+# 32-column pieces), 512 tiles (68 left: 128-column pieces), 474 tiles (30 left: 64-column pieces), 149 tiles with
+# a ragged N (pieces that start beyond N), 150 tiles.
 @pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 128), (1024, 1792, 4096), (384, 200, 72),
-                                   (100, 40, 8), (8192, 4096, 1792)])
+                                   (100, 40, 8), (8192, 4096, 1792),
+                                   (8192, 1792, 512), (4096, 4096, 256), (10112, 1536, 64), (19072, 200, 72),
+                                   (3840, 1280, 128)])
 def test_gemm_matches_fp32_reference(shape):
     from nano_nccl_b200.ops.gemm import gemm_bf16, gemm_last_error
 
