@@ -151,3 +151,36 @@ def test_multi_gpu_rank_choice(monkeypatch):
     assert conftest.multi_gpu_ranks() == 4
     monkeypatch.setattr(conftest, "gpu_count", lambda: 3)
     assert conftest.multi_gpu_ranks() == 2
+
+
+def test_native_table_runs_the_native_programs_with_the_reference_arguments(tmp_path, monkeypatch):
+    """`native_table` with a stand-in launcher and stand-in programs: arguments, host-loop bus bandwidth, notes."""
+    import stat
+    import sys
+
+    from nano_nccl_b200.bench import headline
+
+    log = tmp_path / "calls.log"
+    launcher = tmp_path / "nano_nccl_mpirun"
+    launcher.write_text("#!/bin/sh\nshift 4\nexec \"$@\"\n")
+    row = "{coll}  {dtype} sum  oneshot  1048576  262144  50.00  40.00  41.00  20.97  {bw}  0  0"
+    for name in ("nano_nccl_all_reduce_bench", "nano_nccl_collective_bench"):
+        prog = tmp_path / name
+        prog.write_text(f"#!{sys.executable}\nimport sys\nopen({str(log)!r}, 'a').write(' '.join(sys.argv[1:]) + '\\n')\n"
+                        "a = sys.argv\ncoll = a[a.index('--collective') + 1]\ndtype = a[a.index('--dtype') + 1]\n"
+                        f"print('# header line')\nprint({row!r}.format(coll=coll, dtype=dtype, bw='99.9'))\n"
+                        "sys.exit(3 if coll == 'all_gather' and dtype == 'fp16' else 0)\n")
+    for f in tmp_path.iterdir():
+        f.chmod(f.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setattr(headline, "LIB", tmp_path)
+    t = headline.native_table(4, budget_s=60)
+    assert len(t["cells"]) == 9 and t["wrong_elements"] == 0
+    ar = next(c for c in t["cells"] if c["collective"] == "all_reduce" and c["dtype"] == "bf16")
+    assert ar["busbw_gbs"] == round(1048576 / 50.0 / 1e3 * 2 * 3 / 4, 2)     # from the host time, not the printed column
+    ag = next(c for c in t["cells"] if c["collective"] == "all_gather" and c["dtype"] == "float")
+    assert ag["busbw_gbs"] == round(1048576 / 50.0 / 1e3 * 3 / 4, 2)
+    assert t["notes"] == ["all_gather/fp16: exit 3: # header line | all_gather  fp16 sum  oneshot  1048576  262144  50.00  40.00  41.00  20.97  99.9  0  0"]
+    calls = log.read_text().splitlines()
+    assert len(calls) == 9 and all(c.endswith("-b 262144 -e 67108864 -f 4 -w 5 -n 20") for c in calls)
+    assert all(("--redop sum" in c) == ("all_gather" not in c) for c in calls)
+    assert headline.native_table(4, budget_s=-1)["cells"] == []
